@@ -5,12 +5,15 @@ Layers ask for what they need (`KVRequest`, `StateRequest`); layers with the sam
 form a *group* with storage of its own:
 
   kv group     K, V: [layers in group, pages, kv heads, page_size, head_dim], in the run
-               dtype.  A (page, kv head) is a dense [page_size, head_dim] tile.  Groups are
-               keyed by (kv heads, head_dim, window), so layers that keep all keys and
+               dtype (V with a head size of its own when the request gives one).  A (page,
+               kv head) is a dense [page_size, head_dim] tile.  Groups are keyed by (kv
+               heads, head_dim, window, value head size), so layers that keep all keys and
                layers that look at a window do not share storage.
   state group  [layers in group, slots, *shape]: state of fixed size per sequence, zeroed
-               when the slot is handed out.  The dense decoder has none; the area exists
-               so a mixer with state of its own can be added.
+               when the slot is handed out (a recurrent mixer's matrix state, for one).
+
+A mixer made of several mixers asks for several things at once: a tuple of requests, answered
+by a `CompositeLayer` whose `parts` are the answers in the same order, each in its own group.
 
 All kv groups share one paging (`SlotPager`): position p of a slot lies in page
 `page_table[slot, p // page_size]` at offset `p % page_size`, in every layer.  The
@@ -34,6 +37,7 @@ class KVRequest:
     n_kv_heads: int
     head_dim: int
     window: int | None = None      # None: the layer reads all keys
+    v_head_dim: int | None = None  # None: values have the keys' head size
 
 
 @dataclass(frozen=True)
@@ -53,6 +57,12 @@ class KVLayer:
 class StateLayer:
     state: torch.Tensor            # [slots, *shape]
     request: StateRequest
+
+
+@dataclass
+class CompositeLayer:
+    parts: tuple                   # KVLayer / StateLayer, in the order of the request's members
+    request: tuple
 
 
 class SequenceCache:
@@ -85,26 +95,40 @@ class SequenceCache:
         # group layers by their needs
         self.groups: dict = {}
         self._layers: list = [None] * len(requests)
-        members: dict = {}
+        members: dict = {}                      # request -> [(cache layer, member of a composite or None)]
         for i, req in enumerate(requests):
-            if req is not None:
-                members.setdefault(req, []).append(i)
-        for req, layer_ids in members.items():
+            if isinstance(req, tuple):
+                for m, sub in enumerate(req):
+                    members.setdefault(sub, []).append((i, m))
+                self._layers[i] = CompositeLayer([None] * len(req), req)
+            elif req is not None:
+                members.setdefault(req, []).append((i, None))
+
+        def place(i, m, layer):
+            if m is None:
+                self._layers[i] = layer
+            else:
+                self._layers[i].parts[m] = layer
+
+        for req, users in members.items():
             if isinstance(req, KVRequest):
-                shape = (len(layer_ids), n_pages, req.n_kv_heads, page_size, req.head_dim)
+                shape = (len(users), n_pages, req.n_kv_heads, page_size, req.head_dim)
                 k = torch.zeros(shape, dtype=dtype, device=self.device)
-                v = torch.zeros(shape, dtype=dtype, device=self.device)
+                v = torch.zeros(shape[:-1] + (req.v_head_dim or req.head_dim,), dtype=dtype, device=self.device)
                 self.groups[req] = (k, v)
-                for j, i in enumerate(layer_ids):
-                    self._layers[i] = KVLayer(k[j], v[j], req)
+                for j, (i, m) in enumerate(users):
+                    place(i, m, KVLayer(k[j], v[j], req))
             elif isinstance(req, StateRequest):
-                s = torch.zeros((len(layer_ids), n_slots) + tuple(req.shape), dtype=req.dtype,
+                s = torch.zeros((len(users), n_slots) + tuple(req.shape), dtype=req.dtype,
                                 device=self.device)
                 self.groups[req] = (s,)
-                for j, i in enumerate(layer_ids):
-                    self._layers[i] = StateLayer(s[j], req)
+                for j, (i, m) in enumerate(users):
+                    place(i, m, StateLayer(s[j], req))
             else:
-                raise TypeError(f"cache layer {i}: unknown request {req!r}")
+                raise TypeError(f"cache layers {[i for i, _ in users]}: unknown request {req!r}")
+        for layer in self._layers:
+            if isinstance(layer, CompositeLayer):
+                layer.parts = tuple(layer.parts)
 
     # ---- what the model reads --------------------------------------------
     def layer(self, index: int):

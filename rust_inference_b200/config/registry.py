@@ -50,12 +50,19 @@ def get_architecture(name: str) -> Architecture:
         ) from None
 
 
+def architecture_name(d: Mapping[str, Any]) -> str:
+    """The name config.json gives its model: the first entry of `architectures`, or `architecture`."""
+    archs = d.get("architectures")
+    if isinstance(archs, (list, tuple)) and archs:
+        return str(archs[0])
+    if isinstance(d.get("architecture"), str) and d["architecture"]:
+        return d["architecture"]
+    raise ConfigError("config.json: 'architectures' must be a non-empty list (or 'architecture' a name)")
+
+
 def config_from_dict(d: Mapping[str, Any]):
     """Pick the architecture named by the dict and parse it into that architecture's config."""
-    archs = d.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list")
-    return get_architecture(str(archs[0])).parse_config(d)
+    return get_architecture(architecture_name(d)).parse_config(d)
 
 
 def load_config(model_dir: str):
@@ -66,14 +73,11 @@ def load_spec(model_dir: str):
     """(config, ModelSpec) of a model folder: config.json's architecture name picks the
     architecture, which parses the config and builds the spec."""
     d = read_config_json(model_dir)
-    archs = d.get("architectures")
-    if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json: 'architectures' must be a non-empty list")
-    arch = get_architecture(str(archs[0]))
+    arch = get_architecture(architecture_name(d))
     config = arch.parse_config(d)
     return config, arch.build_spec(config)
 
 
 def _ensure_builtin() -> None:
-    # The dense decoder registers itself on import.
-    from ..models import dense_decoder  # noqa: F401
+    # The built-in models register themselves on import.
+    from ..models import dense_decoder, lulisun  # noqa: F401

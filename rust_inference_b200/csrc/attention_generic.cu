@@ -9,8 +9,11 @@
 // 114-120).  Query head h reads kv head h / (n_heads / n_kv_heads) (attention.rs:95-98).
 // All arithmetic is float32 with accurate expf.
 //
-// `window` > 0 limits the keys to the last `window` positions (p-window+1 .. p); the
-// dense decoder passes 0.
+// `window` > 0 limits the keys to the last `window` positions (p-window+1 .. p); `chunk` > 0
+// limits them to the query's own block of `chunk` positions, counted from position 0 of the
+// sequence (floor(p / chunk) * chunk .. p); the dense decoder passes 0 for both.  Values may
+// have another head size than keys (`v_hd`), and the result is multiplied by `out_scale`
+// before it is rounded to the output type.
 #include "common.cuh"
 
 using namespace ri;
@@ -26,7 +29,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
                     const T* __restrict__ vcache, const int* __restrict__ page_table, int max_pages,
                     const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                     const int* __restrict__ seq_slot, T* __restrict__ out, int out_ld, int n_heads,
-                    int n_kv_heads, int hd, int page_size, float scale, int window) {
+                    int n_kv_heads, int hd, int v_hd, int page_size, float scale, int window, int chunk,
+                    float out_scale) {
     extern __shared__ float smem[];
     float* qs = smem;                 // [hd]
     float* ps = smem + hd;            // [THREADS]
@@ -41,7 +45,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
 
     for (int d = tid; d < hd; d += THREADS) qs[d] = to_f32<T>(q[(size_t)t * q_ld + h * hd + d]);
 
-    const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) first = max(first, pos - pos % chunk);
     const int n_keys = pos + 1;
 
     float m = -INFINITY, l = 0.f;
@@ -75,19 +80,19 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
 #pragma unroll
         for (int a = 0; a < MAX_ACC; ++a) {
             const int d = tid + a * THREADS;
-            if (d < hd) {
+            if (d < v_hd) {
                 float o = acc[a] * alpha;
                 for (int jj = 0; jj < cn; ++jj)
-                    o = fmaf(ps[jj], to_f32<T>(vcache[(size_t)key_off[jj] * hd + d]), o);
+                    o = fmaf(ps[jj], to_f32<T>(vcache[(size_t)key_off[jj] * v_hd + d]), o);
                 acc[a] = o;
             }
         }
     }
-    const float inv = 1.0f / l;
+    const float inv = out_scale / l;
 #pragma unroll
     for (int a = 0; a < MAX_ACC; ++a) {
         const int d = tid + a * THREADS;
-        if (d < hd) out[(size_t)t * out_ld + h * hd + d] = from_f32<T>(acc[a] * inv);
+        if (d < v_hd) out[(size_t)t * out_ld + h * v_hd + d] = from_f32<T>(acc[a] * inv);
     }
 }
 
@@ -96,12 +101,15 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
 RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, const void* vcache,
                                 const int* page_table, int max_pages, const int* token_pos,
                                 const int* token_seq, const int* seq_slot, void* out, int out_ld, int dtype,
-                                int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
-                                long long cache_rows, float scale, int window, cudaStream_t stream) {
+                                int n_tokens, int n_heads, int n_kv_heads, int hd, int v_hd, int page_size,
+                                long long cache_rows, float scale, int window, int chunk, float out_scale,
+                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads)
         return fail("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
-    if (hd > THREADS * MAX_ACC) return fail("attention: head_dim %d exceeds %d", hd, THREADS * MAX_ACC);
+    if (v_hd <= 0) v_hd = hd;
+    if (v_hd > THREADS * MAX_ACC) return fail("attention: value head size %d exceeds %d", v_hd, THREADS * MAX_ACC);
+    if (hd <= 0 || window < 0 || chunk < 0) return fail("attention: head size %d, window %d, chunk %d", hd, window, chunk);
     if (cache_rows > 0x7fffffffLL) return fail("attention: cache of %lld rows exceeds 2^31", cache_rows);
     if (n_heads > 65535) return fail("attention: %d heads exceed the grid limit", n_heads);
     const size_t smem = (size_t)(hd + 2 * THREADS) * sizeof(float);
@@ -109,12 +117,12 @@ RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, con
     if (dtype == RI_F32)
         attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_ld, (const float*)kcache, (const float*)vcache, page_table, max_pages, token_pos,
-            token_seq, seq_slot, (float*)out, out_ld, n_heads, n_kv_heads, hd, page_size, scale, window);
+            token_seq, seq_slot, (float*)out, out_ld, n_heads, n_kv_heads, hd, v_hd, page_size, scale, window, chunk, out_scale);
     else if (dtype == RI_BF16)
         attn_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, page_table,
             max_pages, token_pos, token_seq, seq_slot, (__nv_bfloat16*)out, out_ld, n_heads, n_kv_heads, hd,
-            page_size, scale, window);
+            v_hd, page_size, scale, window, chunk, out_scale);
     else
         return fail("attention: unknown dtype %d", dtype);
     return check_launch("attention_generic");

@@ -225,7 +225,10 @@ RI_API int ri_rmsnorm(const float* x, const float* w, const int* rows, void* out
 // (attention.rs:78-87, rope.rs:88-97); q is rotated in place, rotated k and plain v go
 // to the token's cache position (attention.rs:89-90, kv_cache.rs:52-75).
 //
-// style 0: pairs (i, i + hd/2); style 1: pairs (2i, 2i+1), the reference's.
+// style 0: pairs (i, i + hd/2); style 1: pairs (2i, 2i+1), the reference's.  With `rot` < hd only the
+// first `rot` channels of a head are rotated (pairs (i, i + rot/2) or (2i, 2i+1) within them, the table
+// having rot/2 angles per position) and the rest pass unchanged; values may have a head size of their
+// own (`v_hd`), their cache then being [page][kv head][page_size][v_hd].
 // Cache layer layout: [page][kv head][page_size][hd]; page of position p of sequence b is
 // page_table[slot(b) * max_pages + p / page_size].
 // ----------------------------------------------------------------------------
@@ -236,12 +239,12 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float
                                         const int* __restrict__ page_table, int max_pages,
                                         T* __restrict__ kcache, T* __restrict__ vcache,
                                         int n_heads, int n_kv_heads, int hd, int page_size, int style,
-                                        int write_kv) {
+                                        int write_kv, int rot, int v_hd) {
     const int t = blockIdx.x;
     let_next_kernel_start();
     wait_for_previous_kernels();          // the projections come from the previous kernel
     const int pos = token_pos[t];
-    const int half = hd >> 1;
+    const int half = rot >> 1;
     T* row = qkv + (size_t)t * ld;
     const float* c = cos_t + (size_t)pos * half;
     const float* s = sin_t + (size_t)pos * half;
@@ -256,10 +259,12 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float
         } else {
             const int page = page_table[(size_t)slot * max_pages + pos / page_size];
             if (!RI_BLOCK_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) write_kv = 0;
-            cache_base = ((size_t)page * n_kv_heads * page_size + (pos % page_size)) * hd;
+            cache_base = (size_t)page * n_kv_heads * page_size + (pos % page_size);      // in rows
         }
     }
-    const size_t head_stride = (size_t)page_size * hd;
+    const size_t head_stride = (size_t)page_size * hd, v_head_stride = (size_t)page_size * v_hd;
+    const size_t v_base = cache_base * v_hd;
+    cache_base *= hd;
 
     // q heads: rotate in place
     for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
@@ -283,10 +288,15 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, int ld, const float
         dst[i0] = from_f32<T>(x0 * c[i] - x1 * s[i]);
         dst[i1] = from_f32<T>(x0 * s[i] + x1 * c[i]);
     }
+    // the channels of k beyond the rotated ones: copy
+    for (int idx = threadIdx.x; idx < n_kv_heads * (hd - rot); idx += blockDim.x) {
+        const int h = idx / (hd - rot), d = rot + idx % (hd - rot);
+        kcache[cache_base + h * head_stride + d] = row[q_dim + h * hd + d];
+    }
     // v heads: copy
-    for (int idx = threadIdx.x; idx < kv_dim; idx += blockDim.x) {
-        const int h = idx / hd, d = idx % hd;
-        vcache[cache_base + h * head_stride + d] = row[q_dim + kv_dim + idx];
+    for (int idx = threadIdx.x; idx < n_kv_heads * v_hd; idx += blockDim.x) {
+        const int h = idx / v_hd, d = idx % v_hd;
+        vcache[v_base + h * v_head_stride + d] = row[q_dim + kv_dim + idx];
     }
 }
 
@@ -395,14 +405,16 @@ RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t,
                                const int* token_pos, const int* token_seq, const int* seq_slot,
                                const int* page_table, int max_pages, void* kcache, void* vcache,
                                int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
-                               int style, int write_kv, cudaStream_t stream) {
+                               int style, int write_kv, int rot, int v_hd, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (hd % 2) return fail("rope_cache_write: head_dim %d is odd", hd);
+    if (rot <= 0) rot = hd;
+    if (v_hd <= 0) v_hd = hd;
+    if (rot % 2 || rot > hd) return fail("rope_cache_write: %d rotated channels of a head of %d", rot, hd);
     if (style != 0 && style != 1) return fail("rope_cache_write: unknown style %d", style);
     const int work = n_heads * hd / 2;
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
     cudaError_t e = cudaSuccess;
-    const bool aligned = hd % 16 == 0 && ld % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)kcache % 16 == 0 &&
+    const bool aligned = rot == hd && v_hd == hd && hd % 16 == 0 && ld % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)kcache % 16 == 0 &&
                          (uintptr_t)vcache % 16 == 0 && (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0;
     if (dtype == RI_BF16 && aligned) {
         const int items = (n_heads + n_kv_heads) * hd / 16;
@@ -415,11 +427,11 @@ RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t,
     if (dtype == RI_F32)
         e = launch_dependent(rope_cache_write_kernel<float>, n_tokens, threads, 0, stream,
             (float*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
-            (float*)kcache, (float*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+            (float*)kcache, (float*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv, rot, v_hd);
     else if (dtype == RI_BF16)
         e = launch_dependent(rope_cache_write_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
             (__nv_bfloat16*)qkv, ld, cos_t, sin_t, token_pos, token_seq, seq_slot, page_table, max_pages,
-            (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv);
+            (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_heads, n_kv_heads, hd, page_size, style, write_kv, rot, v_hd);
     else
         return fail("rope_cache_write: unknown dtype %d", dtype);
     return check_launch(e, "rope_cache_write");

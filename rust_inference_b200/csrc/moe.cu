@@ -1,0 +1,338 @@
+// Routed experts (a mixture of small gated feed-forward layers), on the device from the router to
+// the sum, so a step needs nothing from the host:
+//
+//   route     per token: z = W_router h in float32, s = sigmoid(z); choice score = s + correction;
+//             experts form `groups` equal groups of neighbours, a group's score is the sum of its
+//             two largest choice scores, only the `keep` best groups stay eligible (the others count
+//             as minus infinity); the `top` eligible experts with the largest choice scores are
+//             chosen; their weights are their plain scores s divided by the sum of those (+ 1e-20).
+//             Optionally one more number per token: sigmoid(w_gate . h), the gate of a shared expert.
+//   arrange   the (token, choice) pairs listed expert by expert, cut into tiles of rows that belong
+//             to one expert
+//   experts   the grouped contractions on the FFMA pipe with float32 accumulation, any sizes:
+//             act[p] = silu(Wg[e] h) * (Wu[e] h) and y[p] = Wd[e] act[p] for pair p of expert e
+//   combine   residual[t] += sum_c weight[t, c] * y[t * top + c] (+ gate[t] * shared[t]), in a fixed order
+//
+// A pair is p = token * top + choice; its rows of act and y sit at p, so the order of the lists
+// decides only which block works on which rows.
+#include "common.cuh"
+
+using namespace ri;
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_f32(float x) {
+    if (x >= 0.f) return 1.f / (1.f + expf(-x));
+    const float e = expf(x);
+    return e / (1.f + e);
+}
+
+// (value, index) maximum over a warp; ties go to the lower index.
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+    }
+}
+
+constexpr int ROUTE_WARPS = 4;
+
+// One warp per token.  Shared memory per warp: score[E], choice[E], group score[G].
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+                 const float* __restrict__ gate_w, int* __restrict__ ids, float* __restrict__ weights,
+                 float* __restrict__ gate_out, int n_tokens, int width, int experts, int top, int groups, int keep) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* score = smem + (size_t)warp * (2 * experts + groups);
+    float* choice = score + experts;
+    float* gscore = choice + experts;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= n_tokens) return;
+    const T* h = x + (size_t)t * width;
+
+    for (int e = 0; e < experts; ++e) {
+        const float* w = router + (size_t)e * width;
+        float acc = 0.f;
+        for (int d = lane; d < width; d += 32) acc = fmaf(to_f32<T>(h[d]), w[d], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float s = sigmoid_f32(acc);
+            score[e] = s;
+            choice[e] = s + correction[e];
+        }
+    }
+    if (gate_w != nullptr) {
+        float acc = 0.f;
+        for (int d = lane; d < width; d += 32) acc = fmaf(to_f32<T>(h[d]), gate_w[d], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) gate_out[t] = sigmoid_f32(acc);
+    }
+    __syncwarp();
+
+    // groups: the sum of a group's two largest choice scores; all but the `keep` best are shut out
+    const int size = experts / groups;
+    if (keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;
+            for (int k = 0; k < size; ++k) {
+                const float c = choice[g * size + k];
+                if (c > a) { b = a; a = c; } else if (c > b) { b = c; }
+            }
+            gscore[g] = size > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // `keep` rounds of taking the best remaining group; a taken group is marked with +inf
+        for (int round = 0; round < keep; ++round) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = gscore[g];
+                if (v != INFINITY && (v > bv || (v == bv && g < bi))) { bv = v; bi = g; }
+            }
+            warp_argmax(bv, bi);
+            if (lane == 0 && bi < groups) gscore[bi] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < experts; e += 32)
+            if (gscore[e / size] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
+
+    // `top` rounds of taking the best remaining expert
+    float sum = 0.f;
+    for (int c = 0; c < top; ++c) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = choice[e];              // NaN: taken already; -inf: shut out with its group
+            if (v > bv || (v == bv && v != -INFINITY && e < bi)) { bv = v; bi = e; }
+        }
+        warp_argmax(bv, bi);
+        if (bi >= experts) bi = 0;
+        const float s = score[bi];
+        sum += s;
+        if (lane == 0) {
+            ids[(size_t)t * top + c] = bi;
+            weights[(size_t)t * top + c] = s;
+            choice[bi] = NAN;                    // taken
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / (sum + 1e-20f);
+    for (int c = lane; c < top; c += 32) weights[(size_t)t * top + c] *= inv;
+}
+
+// ---- arrange ---------------------------------------------------------------------------------
+// One block.  offsets[e]..offsets[e+1] index `order`, which lists the pairs of expert e; tiles[2k],
+// tiles[2k+1] = (expert, first index into `order`) of tile k, each tile holding at most `tile_rows`
+// pairs of one expert; n_tiles[0] their number.
+__global__ void __launch_bounds__(1024)
+moe_arrange_kernel(const int* __restrict__ ids, int n_pairs, int experts, int tile_rows, int* __restrict__ offsets,
+                   int* __restrict__ order, int* __restrict__ tiles, int* __restrict__ n_tiles) {
+    extern __shared__ int sh[];
+    int* count = sh;                 // [experts]
+    int* start = sh + experts;       // [experts + 1]
+    int* fill = start + experts + 1; // [experts]
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) { count[e] = 0; fill[e] = 0; }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0, nt = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = acc;
+            for (int r0 = 0; r0 < count[e]; r0 += tile_rows) {
+                tiles[2 * nt] = e;
+                tiles[2 * nt + 1] = acc + r0;
+                ++nt;
+            }
+            acc += count[e];
+        }
+        start[experts] = acc;
+        n_tiles[0] = nt;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
+    // a pair's place among its expert's pairs is whatever the atomics hand out: every pair owns its rows
+    // of the results, so the order changes no number
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < experts) order[start[e] + atomicAdd(&fill[e], 1)] = p;
+    }
+}
+
+// ---- the grouped contractions ------------------------------------------------------------------
+constexpr int GM = 32, GN = 64, GK = 16, G_THREADS = 256;      // a tile of 32 pairs x 64 features; thread: 2 x 4
+
+// GATE: act[p, n] = silu(sum_k Wg[e][n, k] x[p / top, k]) * (sum_k Wu[e][n, k] x[p / top, k])   (T out)
+// else: y[p, n]   = sum_k Wd[e][n, k] act[p, k]                                                  (float out)
+template <typename T, bool GATE>
+__global__ void __launch_bounds__(G_THREADS)
+moe_grouped_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __restrict__ W2, void* __restrict__ out_,
+                   const int* __restrict__ offsets, const int* __restrict__ order, const int* __restrict__ tiles,
+                   const int* __restrict__ n_tiles, int top, int N, int K) {
+    __shared__ float Xs[GK][GM + 1];
+    __shared__ float Ws[GK][GN + 1];
+    __shared__ float W2s[GATE ? GK : 1][GATE ? GN + 1 : 1];
+    __shared__ int rows[GM];
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    if ((int)blockIdx.x >= n_tiles[0]) return;
+    const int e = tiles[2 * blockIdx.x], first = tiles[2 * blockIdx.x + 1];
+    const int n_rows = min(GM, offsets[e + 1] - first);
+    const int n0 = blockIdx.y * GN;
+    const int tid = threadIdx.x;
+    if (tid < GM) rows[tid] = tid < n_rows ? order[first + tid] : -1;
+    __syncthreads();
+    const T* We = W + (size_t)e * N * K;
+    const T* W2e = GATE ? W2 + (size_t)e * N * K : nullptr;
+    const int tm = (tid / 16) * 2, tn = (tid % 16) * 4;
+    float acc[2][4] = {}, acc2[2][4] = {};
+    for (int k0 = 0; k0 < K; k0 += GK) {
+        // X tile: GM x GK
+        for (int i = tid; i < GM * GK; i += G_THREADS) {
+            const int m = i / GK, k = i % GK;
+            const int p = rows[m];
+            float v = 0.f;
+            if (p >= 0 && k0 + k < K) v = to_f32<T>(X[(size_t)(GATE ? p / top : p) * K + k0 + k]);
+            Xs[k][m] = v;
+        }
+        for (int i = tid; i < GN * GK; i += G_THREADS) {
+            const int n = i / GK, k = i % GK;
+            const bool in = n0 + n < N && k0 + k < K;
+            Ws[k][n] = in ? to_f32<T>(We[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+            if (GATE) W2s[k][n] = in ? to_f32<T>(W2e[(size_t)(n0 + n) * K + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < GK; ++k) {
+            float xv[2], wv[4], w2v[4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a) xv[a] = Xs[k][tm + a];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                wv[b] = Ws[k][tn + b];
+                if (GATE) w2v[b] = W2s[k][tn + b];
+            }
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    acc[a][b] = fmaf(xv[a], wv[b], acc[a][b]);
+                    if (GATE) acc2[a][b] = fmaf(xv[a], w2v[b], acc2[a][b]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        const int p = rows[tm + a];
+        if (p < 0) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int n = n0 + tn + b;
+            if (n >= N) continue;
+            if (GATE)
+                reinterpret_cast<T*>(out_)[(size_t)p * N + n] = from_f32<T>(silu_f32(acc[a][b]) * acc2[a][b]);
+            else
+                reinterpret_cast<float*>(out_)[(size_t)p * N + n] = acc[a][b];
+        }
+    }
+}
+
+__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ y,
+                                   const float* __restrict__ weights, const float* __restrict__ shared_y,
+                                   const float* __restrict__ gate, int n_tokens, int width, int top) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const size_t total = (size_t)n_tokens * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / width), d = (int)(i % width);
+        float acc = 0.f;
+        for (int c = 0; c < top; ++c)
+            acc = fmaf(weights[(size_t)t * top + c], y[((size_t)t * top + c) * width + d], acc);
+        if (shared_y != nullptr) acc = fmaf(gate[t], shared_y[i], acc);
+        residual[i] += acc;
+    }
+}
+
+}  // namespace
+
+RI_API int ri_moe_route(const void* x, int dtype, const float* router, const float* correction, const float* gate_w,
+                        int* ids, float* weights, float* gate_out, int n_tokens, int width, int experts, int top,
+                        int groups, int keep, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (experts <= 0 || top <= 0 || top > experts) return fail("moe_route: top %d of %d experts", top, experts);
+    if (groups <= 0 || experts % groups || keep <= 0 || keep > groups)
+        return fail("moe_route: %d experts in %d groups, %d kept", experts, groups, keep);
+    if ((long long)keep * (experts / groups) < top)
+        return fail("moe_route: %d groups of %d experts cannot give %d choices", keep, experts / groups, top);
+    const size_t smem = (size_t)ROUTE_WARPS * (2 * experts + groups) * sizeof(float);
+    if (smem > 48 * 1024) return fail("moe_route: %d experts exceed the router kernel's shared memory", experts);
+    const int blocks = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    cudaError_t e;
+    if (dtype == RI_F32)
+        e = launch_dependent(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, router,
+                             correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top, groups, keep);
+    else if (dtype == RI_BF16)
+        e = launch_dependent(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream,
+                             (const __nv_bfloat16*)x, router, correction, gate_w, ids, weights, gate_out, n_tokens, width,
+                             experts, top, groups, keep);
+    else
+        return fail("moe_route: unknown dtype %d", dtype);
+    return check_launch(e, "moe_route");
+}
+
+RI_API int ri_moe_tile_rows() { return GM; }
+
+RI_API int ri_moe_arrange(const int* ids, int n_pairs, int experts, int tile_rows, int* offsets, int* order, int* tiles,
+                          int* n_tiles, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (tile_rows <= 0) return fail("moe_arrange: tile of %d rows", tile_rows);
+    const size_t smem = (size_t)(3 * experts + 1) * sizeof(int);
+    if (smem > 48 * 1024) return fail("moe_arrange: %d experts exceed the kernel's shared memory", experts);
+    cudaError_t e = launch_dependent(moe_arrange_kernel, 1, 1024, smem, stream, ids, n_pairs, experts, tile_rows, offsets,
+                                     order, tiles, n_tiles);
+    return check_launch(e, "moe_arrange");
+}
+
+// gate != 0: x [tokens, K], w / w2 [experts, N, K] -> out<dtype> [pairs, N]; else x [pairs, K], w -> out<float> [pairs, N]
+RI_API int ri_moe_grouped_simt(const void* x, const void* w, const void* w2, void* out, int dtype, int gate,
+                               const int* offsets, const int* order, const int* tiles, const int* n_tiles, int n_pairs,
+                               int experts, int top, int N, int K, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    const int max_tiles = (n_pairs + GM - 1) / GM + experts;
+    dim3 grid(max_tiles, (N + GN - 1) / GN);
+    if (grid.y > 65535) return fail("moe_grouped: %d features exceed the grid limit", N);
+    cudaError_t e;
+#define RI_GROUPED(T, G) launch_dependent(moe_grouped_kernel<T, G>, grid, G_THREADS, 0, stream, (const T*)x, (const T*)w, \
+                                          (const T*)w2, out, offsets, order, tiles, n_tiles, top, N, K)
+    if (dtype == RI_F32) e = gate ? RI_GROUPED(float, true) : RI_GROUPED(float, false);
+    else if (dtype == RI_BF16) e = gate ? RI_GROUPED(__nv_bfloat16, true) : RI_GROUPED(__nv_bfloat16, false);
+    else return fail("moe_grouped: unknown dtype %d", dtype);
+#undef RI_GROUPED
+    return check_launch(e, "moe_grouped");
+}
+
+RI_API int ri_moe_combine(float* residual, const float* y, const float* weights, const float* shared_y, const float* gate,
+                          int n_tokens, int width, int top, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const size_t total = (size_t)n_tokens * width;
+    const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    cudaError_t e = launch_dependent(moe_combine_kernel, blocks, 256, 0, stream, residual, y, weights, shared_y, gate,
+                                     n_tokens, width, top);
+    return check_launch(e, "moe_combine");
+}
+
+RI_DEFINE_LAST_ERROR()

@@ -25,14 +25,17 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time (padding not counted)")
     args = ap.parse_args(argv)
 
     from .engine import Engine   # imports torch; compiles kernels at first use
 
     os.makedirs(args.out, exist_ok=True)
     print(f"[trace_run] loading {args.model} ({args.dtype})", file=sys.stderr, flush=True)
-    engine = Engine.from_pretrained(args.model, dtype=args.dtype, device="cuda", max_tokens=args.max_tokens)
+    # a request holds whole pages: room for the last, partly filled page of up to 64 live requests on top
+    from ..cache.sequence_cache import PAGE_SIZE
+    engine = Engine.from_pretrained(args.model, dtype=args.dtype, device="cuda",
+                                    max_tokens=args.max_tokens + 64 * PAGE_SIZE)
     slots: dict = {}
 
     for line in sys.stdin:

@@ -76,11 +76,15 @@ def decode_kernel(name: str):
     return ops.attention_decode
 
 
-def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scale, window=0):
+def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scale, window=0, chunk=0,
+              v_head_dim=None, out_scale=1.0):
     """out[t] = softmax(q_t K^T * scale) V over the keys 0..pos(t) of t's slot.  q is the
-    leading n_heads*head_dim columns of `qkv`, already rotated."""
+    leading n_heads*head_dim columns of `qkv`, already rotated.  `chunk`: only the keys of the
+    query's own block of that many positions; `v_head_dim`: values of another head size than
+    keys; `out_scale`: a factor on the result.  Those three are the generic kernel's."""
     q_ld = qkv.shape[1]
-    if qkv.dtype == torch.bfloat16:
+    plain = not chunk and (v_head_dim is None or v_head_dim == head_dim) and out_scale == 1.0
+    if qkv.dtype == torch.bfloat16 and plain:
         decode = ctx.all_single
         if ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, decode):
             if decode:
@@ -109,4 +113,5 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
     return ops.attention_generic(
         qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.token_pos, ctx.token_seq,
         ctx.seq_slot, out, n_tokens=qkv.shape[0], n_heads=n_heads, n_kv_heads=n_kv_heads,
-        head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window)
+        head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, chunk=chunk or 0,
+        v_head_dim=v_head_dim, out_scale=out_scale)

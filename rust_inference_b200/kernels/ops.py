@@ -192,23 +192,32 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 def rope_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_pos, token_seq,
                      seq_slot, page_table: torch.Tensor, kcache, vcache, *, n_heads: int,
-                     n_kv_heads: int, head_dim: int, page_size: int, style: int, write_kv: bool) -> None:
+                     n_kv_heads: int, head_dim: int, page_size: int, style: int, write_kv: bool,
+                     rot_dims: int | None = None, v_head_dim: int | None = None) -> None:
     """Rotate q (in place) and k by the table rows of each token's position; store rotated k and v
-    at the token's cache position.  kcache/vcache: one layer, [pages, kv heads, page_size, head_dim]."""
+    at the token's cache position.  kcache: one layer, [pages, kv heads, page_size, head_dim]; vcache
+    the same with v_head_dim (default: head_dim).  rot_dims: only the first so many channels of a
+    head are rotated (default: all), the tables then having rot_dims/2 columns."""
     _need_cuda(qkv, cos, sin, token_pos, token_seq, seq_slot, page_table, kcache, vcache)
     n = qkv.shape[0]
-    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim,
-          "rope_cache_write: qkv must be [T, (heads + 2 kv heads) * head_dim]")
-    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == head_dim // 2,
-          "rope_cache_write: tables must be float32 [positions, head_dim/2]")
+    rot = head_dim if rot_dims is None else int(rot_dims)
+    v_hd = head_dim if v_head_dim is None else int(v_head_dim)
+    _need(qkv.is_contiguous() and qkv.shape[1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_hd,
+          "rope_cache_write: qkv must be [T, (heads + kv heads) * head_dim + kv heads * value head size]")
+    _need(0 < rot <= head_dim and rot % 2 == 0, "rope_cache_write: rotated channels must be even and at most head_dim")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot // 2
+          and cos.is_contiguous() and sin.is_contiguous(),
+          "rope_cache_write: tables must be float32 [positions, rotated channels / 2]")
     if write_kv:
         _need(kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous()
               and vcache.is_contiguous(), "rope_cache_write: cache dtype/layout")
-        _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim), "rope_cache_write: cache shape")
+        _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim)
+              and tuple(vcache.shape[1:]) == (n_kv_heads, page_size, v_hd), "rope_cache_write: cache shape")
     _call("elementwise", "ri_rope_cache_write", _p(qkv), c_int(dtype_code(qkv.dtype)), c_int(qkv.shape[1]),
           _p(cos), _p(sin), _p(token_pos), _p(token_seq), _p(seq_slot), _p(page_table),
           c_int(page_table.shape[1]), _p(kcache), _p(vcache), c_int(n), c_int(n_heads), c_int(n_kv_heads),
-          c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), _stream())
+          c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), c_int(rot), c_int(v_hd),
+          _stream())
 
 
 def rope_cache_write_acc(acc: torch.Tensor, bias, q_out: torch.Tensor, cos, sin, token_pos, token_seq, seq_slot,
@@ -267,17 +276,24 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
 
 def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, token_pos, token_seq,
                       seq_slot, out: torch.Tensor, *, n_tokens: int, n_heads: int, n_kv_heads: int,
-                      head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
-    """Attention of every given token over its slot's cached keys 0..position (any sizes)."""
+                      head_dim: int, page_size: int, scale: float, window: int = 0, chunk: int = 0,
+                      v_head_dim: int | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    """Attention of every given token over its slot's cached keys 0..position (any sizes), limited to
+    the last `window` keys and / or to the query's own block of `chunk` positions when those are not 0;
+    values of head size v_head_dim (default: head_dim); the result times out_scale."""
     _need_cuda(q, kcache, vcache, page_table, token_pos, token_seq, seq_slot, out)
     _need(q.dtype == kcache.dtype == vcache.dtype == out.dtype, "attention: dtypes differ")
-    _need(out.is_contiguous() and out.shape == (n_tokens, n_heads * head_dim), "attention: out shape")
+    v_hd = head_dim if v_head_dim is None else int(v_head_dim)
+    _need(out.is_contiguous() and out.shape == (n_tokens, n_heads * v_hd), "attention: out shape")
+    _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim)
+          and tuple(vcache.shape[1:]) == (n_kv_heads, page_size, v_hd) and kcache.shape[0] == vcache.shape[0],
+          "attention: cache shape")
     rows = kcache.shape[0] * kcache.shape[1] * kcache.shape[2]
     _call("attention_generic", "ri_attention_generic", _p(q), c_int(q_ld), _p(kcache), _p(vcache),
           _p(page_table), c_int(page_table.shape[1]), _p(token_pos), _p(token_seq), _p(seq_slot), _p(out),
           c_int(out.shape[1]), c_int(dtype_code(q.dtype)), c_int(n_tokens), c_int(n_heads),
-          c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_longlong(rows), c_float(scale),
-          c_int(window), _stream())
+          c_int(n_kv_heads), c_int(head_dim), c_int(v_hd), c_int(page_size), c_longlong(rows), c_float(scale),
+          c_int(window), c_int(chunk), c_float(out_scale), _stream())
     return out
 
 
@@ -410,3 +426,109 @@ def attention_prefill(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, se
           c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
           c_float(scale), c_int(window), _stream())
     return out
+
+
+# ----------------------------------------------------------------------------
+# A gated linear recurrence with a matrix state per head (csrc/recurrent.cu)
+# ----------------------------------------------------------------------------
+def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, norm_weight: torch.Tensor,
+                     state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, *,
+                     n_seqs: int, heads: int, dim: int, vdim: int, eps: float, out_scale: float = 1.0) -> torch.Tensor:
+    """S <- diag(f) S + (1 - f) v^T, o = S^T q per head over every sequence's new tokens in order, then
+    o / rms(o) * norm_weight * out_scale per head.  z: float32 [T, 2*heads*dim + heads*vdim] holding the
+    projections [q | f | v] before their activations (overwritten); state: float32 [slots, heads, dim,
+    vdim], read and left at the sequence's last token; out: [T, heads*vdim] in the run dtype."""
+    _need_cuda(z, bias, lower, norm_weight, state, cu_seqlens, seq_slot, out)
+    n = z.shape[0]
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.shape[1] == 2 * heads * dim + heads * vdim,
+          "gated_recurrence: z must be float32 [T, 2*heads*dim + heads*vdim]")
+    for t, size in ((bias, heads * dim), (lower, heads * dim), (norm_weight, vdim)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == size, "gated_recurrence: float32 vectors")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "gated_recurrence: state must be float32 [slots, heads, dim, vdim]")
+    _need(out.is_contiguous() and out.shape == (n, heads * vdim), "gated_recurrence: out shape")
+    _need(cu_seqlens.dtype == torch.int32 and seq_slot.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
+          and seq_slot.numel() >= n_seqs, "gated_recurrence: the step's arrays must be int32")
+    _call("recurrent", "ri_gated_recurrence", _p(z), c_int(z.shape[1]), _p(bias), _p(lower), _p(norm_weight), _p(state),
+          _p(cu_seqlens), _p(seq_slot), _p(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(n_seqs), c_int(heads),
+          c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), _stream())
+    global _launches
+    _launches += 2                    # three kernels behind one entry point
+    return out
+
+
+# ----------------------------------------------------------------------------
+# Routed experts (csrc/moe.cu)
+# ----------------------------------------------------------------------------
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, ids: torch.Tensor,
+              weights: torch.Tensor, *, top: int, groups: int = 1, keep: int = 1,
+              gate_weight: torch.Tensor | None = None, gate_out: torch.Tensor | None = None) -> None:
+    """Per token the `top` experts with the largest sigmoid(router x) + correction among the `keep` best of
+    `groups` groups (a group's score: the sum of its two largest), ids int32 [T, top], and their weights
+    float32 [T, top] (the plain sigmoid scores, normalised).  gate_weight float32 [width]: gate_out[t] =
+    sigmoid(gate_weight . x_t) as well."""
+    _need_cuda(x, router, correction, ids, weights, gate_weight, gate_out)
+    n, width = x.shape
+    experts = router.shape[0]
+    _need(x.is_contiguous() and router.dtype == torch.float32 and router.is_contiguous() and router.shape[1] == width
+          and correction.dtype == torch.float32 and correction.numel() == experts, "moe_route: router and correction")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and ids.numel() >= n * top and weights.dtype == torch.float32
+          and weights.is_contiguous() and weights.numel() >= n * top, "moe_route: ids int32 and weights float32 [T, top]")
+    _need((gate_weight is None) == (gate_out is None), "moe_route: gate weight and output go together")
+    if gate_weight is not None:
+        _need(gate_weight.dtype == torch.float32 and gate_weight.is_contiguous() and gate_weight.numel() == width
+              and gate_out.dtype == torch.float32 and gate_out.numel() >= n, "moe_route: gate")
+    _call("moe", "ri_moe_route", _p(x), c_int(dtype_code(x.dtype)), _p(router), _p(correction), _p(gate_weight), _p(ids),
+          _p(weights), _p(gate_out), c_int(n), c_int(width), c_int(experts), c_int(top), c_int(groups), c_int(keep),
+          _stream())
+
+
+def moe_tile_rows() -> int:
+    return int(load("moe").ri_moe_tile_rows())
+
+
+def moe_arrange(ids: torch.Tensor, n_pairs: int, experts: int, tile_rows: int, offsets: torch.Tensor,
+                order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """The (token, choice) pairs listed expert by expert (`offsets` int32 [experts + 1] into `order` int32
+    [pairs]) and cut into tiles of at most tile_rows pairs of one expert (`tiles` int32 [2 * (pairs /
+    tile_rows + experts)]: expert and first index; `n_tiles` int32 [1])."""
+    _need_cuda(ids, offsets, order, tiles, n_tiles)
+    for t in (ids, offsets, order, tiles, n_tiles):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), "moe_arrange: int32 arrays")
+    _need(offsets.numel() >= experts + 1 and order.numel() >= n_pairs
+          and tiles.numel() >= 2 * (-(-n_pairs // tile_rows) + experts), "moe_arrange: arrays too small")
+    _call("moe", "ri_moe_arrange", _p(ids), c_int(n_pairs), c_int(experts), c_int(tile_rows), _p(offsets), _p(order),
+          _p(tiles), _p(n_tiles), _stream())
+
+
+def moe_grouped_simt(x: torch.Tensor, w: torch.Tensor, w2: torch.Tensor | None, out: torch.Tensor, offsets, order,
+                     tiles, n_tiles, *, n_pairs: int, top: int) -> torch.Tensor:
+    """The experts' contractions over the arranged pairs, on the FFMA pipe.  With w2: x [T, K], w and w2
+    [experts, N, K], out[p] = silu(w[e] x[p // top]) * (w2[e] x[p // top]) in the run dtype; without:
+    x [pairs, K], out[p] = w[e] x[p] in float32."""
+    _need_cuda(x, w, w2, out, offsets, order, tiles, n_tiles)
+    experts, n, k = w.shape
+    gate = w2 is not None
+    _need(x.dtype == w.dtype and x.is_contiguous() and w.is_contiguous() and x.shape[1] == k, "moe_grouped: x and w")
+    _need(not gate or (w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous()), "moe_grouped: second matrix")
+    _need(out.is_contiguous() and out.shape == (n_pairs, n) and out.dtype == (x.dtype if gate else torch.float32),
+          "moe_grouped: out")
+    _need(x.shape[0] * (top if gate else 1) >= n_pairs, "moe_grouped: fewer rows than pairs")
+    _call("moe", "ri_moe_grouped_simt", _p(x), _p(w), _p(w2), _p(out), c_int(dtype_code(x.dtype)), c_int(1 if gate else 0),
+          _p(offsets), _p(order), _p(tiles), _p(n_tiles), c_int(n_pairs), c_int(experts), c_int(top), c_int(n), c_int(k),
+          _stream())
+    return out
+
+
+def moe_combine(residual: torch.Tensor, y: torch.Tensor, weights: torch.Tensor, *, top: int,
+                shared_y: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> None:
+    """residual[t] += sum_c weights[t, c] * y[t * top + c] (+ gate[t] * shared_y[t]); all float32."""
+    _need_cuda(residual, y, weights, shared_y, gate)
+    n, width = residual.shape
+    for t in (residual, y, weights, shared_y, gate):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "moe_combine: float32 tensors")
+    _need(y.shape == (n * top, width) and weights.numel() >= n * top, "moe_combine: shapes")
+    _need((shared_y is None) == (gate is None) and (shared_y is None or (shared_y.shape == (n, width) and gate.numel() >= n)),
+          "moe_combine: the shared result and its gate go together")
+    _call("moe", "ri_moe_combine", _p(residual), _p(y), _p(weights), _p(shared_y), _p(gate), c_int(n), c_int(width),
+          c_int(top), _stream())

@@ -20,63 +20,81 @@ class GQAttention(Mixer):
     kv head h / (heads / kv heads) (:37, :96), and the output projection without bias added
     onto the residual stream (:123, transformer.rs:38-39)."""
 
+    # Beyond the dense decoder's form, as parameters: values of a head size of their own (`v_head_dim`),
+    # a score scale other than 1/sqrt(head_dim) (`scale`), keys limited to the query's own block of
+    # `chunk` positions counted from the start of the sequence, a factor on the mixer's result
+    # (`out_scale`, applied to the attention's output in float32 before the output projection), and
+    # the tensors' names below the part's prefix (`names`: q, k, v, o and, with biases, q_bias, ...).
+    _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+              "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
+
     def __init__(self, *, n_heads: int, n_kv_heads: int, head_dim: int, qkv_bias: bool,
-                 position: PartSpec, window: int | None = None, hidden_size: int, dtype, device):
+                 position: PartSpec, window: int | None = None, v_head_dim: int | None = None,
+                 scale: float | None = None, chunk: int | None = None, out_scale: float = 1.0,
+                 names: dict | None = None, hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
+        if chunk is not None and chunk <= 0:
+            raise ValueError(f"a chunk holds at least one position, found {chunk}")
         self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
+        self.v_head_dim = head_dim if v_head_dim is None else int(v_head_dim)
         self.q_dim, self.kv_dim = n_heads * head_dim, n_kv_heads * head_dim
+        self.v_dim, self.o_dim = n_kv_heads * self.v_head_dim, n_heads * self.v_head_dim
         self.qkv_bias = bool(qkv_bias)
         self.window = window
-        self.scale = 1.0 / math.sqrt(float(head_dim))
+        self.chunk = chunk
+        self.out_scale = float(out_scale)
+        self.scale = 1.0 / math.sqrt(float(head_dim)) if scale is None else float(scale)
+        self.names = dict(self._NAMES, **(names or {}))
         self.position = lookup("position", position.kind)(
             hidden_size=hidden_size, dtype=dtype, device=device, **position.params)
         self.w_qkv = self.b_qkv = self.w_o = None
 
     def tensor_specs(self):
-        h = self.hidden_size
+        h, nm = self.hidden_size, self.names
         specs = {
-            "q_proj.weight": TensorSpec((self.q_dim, h)),
-            "k_proj.weight": TensorSpec((self.kv_dim, h)),
-            "v_proj.weight": TensorSpec((self.kv_dim, h)),
-            "o_proj.weight": TensorSpec((h, self.q_dim)),
+            nm["q"]: TensorSpec((self.q_dim, h)),
+            nm["k"]: TensorSpec((self.kv_dim, h)),
+            nm["v"]: TensorSpec((self.v_dim, h)),
+            nm["o"]: TensorSpec((h, self.o_dim)),
         }
         if self.qkv_bias:
-            specs["q_proj.bias"] = TensorSpec((self.q_dim,), role="vector")
-            specs["k_proj.bias"] = TensorSpec((self.kv_dim,), role="vector")
-            specs["v_proj.bias"] = TensorSpec((self.kv_dim,), role="vector")
+            specs[nm["q_bias"]] = TensorSpec((self.q_dim,), role="vector")
+            specs[nm["k_bias"]] = TensorSpec((self.kv_dim,), role="vector")
+            specs[nm["v_bias"]] = TensorSpec((self.v_dim,), role="vector")
         return specs
 
     def set_tensors(self, tensors):
+        nm = self.names
         # one matrix for the three projections: one pass over x
-        self.w_qkv = linear.Weight(torch.cat(
-            [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0))
+        self.w_qkv = linear.Weight(torch.cat([tensors[nm["q"]], tensors[nm["k"]], tensors[nm["v"]]], dim=0))
         if self.qkv_bias:
-            self.b_qkv = torch.cat(
-                [tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]], dim=0).contiguous()
-        self.w_o = linear.Weight(tensors["o_proj.weight"])
+            self.b_qkv = torch.cat([tensors[nm["q_bias"]], tensors[nm["k_bias"]], tensors[nm["v_bias"]]],
+                                   dim=0).contiguous()
+        self.w_o = linear.Weight(tensors[nm["o"]])
 
     def get_tensors(self):
-        q, kv = self.q_dim, self.kv_dim
+        q, kv, nm = self.q_dim, self.kv_dim, self.names
         w = self.w_qkv.t
-        out = {"q_proj.weight": w[:q], "k_proj.weight": w[q:q + kv], "v_proj.weight": w[q + kv:],
-               "o_proj.weight": self.w_o.t}
+        out = {nm["q"]: w[:q], nm["k"]: w[q:q + kv], nm["v"]: w[q + kv:], nm["o"]: self.w_o.t}
         if self.qkv_bias:
             b = self.b_qkv
-            out.update({"q_proj.bias": b[:q], "k_proj.bias": b[q:q + kv], "v_proj.bias": b[q + kv:]})
+            out.update({nm["q_bias"]: b[:q], nm["k_bias"]: b[q:q + kv], nm["v_bias"]: b[q + kv:]})
         return out
 
     def prepare(self, max_positions):
         self.position.prepare(max_positions)
 
     def cache_request(self):
-        return KVRequest(self.n_kv_heads, self.head_dim, self.window)
+        return KVRequest(self.n_kv_heads, self.head_dim, self.window,
+                         None if self.v_head_dim == self.head_dim else self.v_head_dim)
 
     def forward(self, x, residual, ctx, cache_layer, writes_cache):
         n = x.shape[0]
-        width = self.q_dim + 2 * self.kv_dim
-        from_acc = getattr(self.position, "apply_and_store_from_accumulators", None)
+        width = self.q_dim + self.kv_dim + self.v_dim
+        usual = self.v_head_dim == self.head_dim and not getattr(self.position, "partial", False)
+        from_acc = getattr(self.position, "apply_and_store_from_accumulators", None) if usual else None
         if from_acc is not None and linear.wants_split(x, self.w_qkv):
             # a small step: the projection is split over K into float32 accumulators, and the
             # position encoding adds the bias, rotates and stores from there
@@ -88,11 +106,13 @@ class GQAttention(Mixer):
         else:
             qkv = ctx.buffer("qkv", (n, width), self.dtype)
             linear.project(x, self.w_qkv, qkv, ctx, bias=self.b_qkv)
+            extra = {} if usual else {"v_head_dim": self.v_head_dim}
             self.position.apply_and_store(qkv, ctx, cache_layer, n_heads=self.n_heads,
                                           n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
-                                          write_kv=writes_cache)
-        mixed = ctx.buffer("attn_out", (n, self.q_dim), self.dtype)
+                                          write_kv=writes_cache, **extra)
+        mixed = ctx.buffer("attn_out", (n, self.o_dim), self.dtype)
         attn_kernels.attention(qkv, cache_layer, mixed, ctx, n_heads=self.n_heads,
                                n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale,
-                               window=self.window or 0)
+                               window=self.window or 0, chunk=self.chunk or 0, v_head_dim=self.v_head_dim,
+                               out_scale=self.out_scale)
         linear.into_residual(mixed, self.w_o, residual, ctx)

@@ -18,3 +18,25 @@ class PreNorm(Arrangement):
         self.mixer.forward(normed, residual, ctx, cache_layer, writes_cache)
         self.feed_forward_norm.forward(residual, normed)
         self.feed_forward.forward(normed, residual, ctx)
+
+
+@register("arrangement", "parallel_two_norms")
+class ParallelTwoNorms(Arrangement):
+    """x <- x + mixer(norm_a(x)) + ff(norm_b(x)): mixer and feed-forward read the same stream, each
+    through a norm of its own; both add onto the float32 stream.  A layer may have no feed-forward
+    (then it has no second norm either)."""
+
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+    OPTIONAL = ("feed_forward", "feed_forward_norm")
+
+    def forward(self, residual, ctx, cache_layer, writes_cache):
+        shape = (residual.shape[0], residual.shape[1])
+        normed = ctx.buffer("normed", shape, ctx.dtype)
+        self.mixer_norm.forward(residual, normed)
+        if self.feed_forward is not None:
+            # both norms read the stream before either branch adds to it
+            normed_ff = ctx.buffer("normed_ff", shape, ctx.dtype)
+            self.feed_forward_norm.forward(residual, normed_ff)
+        self.mixer.forward(normed, residual, ctx, cache_layer, writes_cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(normed_ff, residual, ctx)

@@ -9,19 +9,20 @@ from .spec import TensorSpec
 
 @register("embedding", "token_embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, *, vocab_size: int, hidden_size: int, dtype, device):
+    def __init__(self, *, vocab_size: int, weight_name: str = "weight", hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         self.vocab_size = vocab_size
+        self.weight_name = weight_name      # the table's name below the part's prefix
         self.weight = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
+        return {self.weight_name: TensorSpec((self.vocab_size, self.hidden_size))}
 
     def set_tensors(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
 
     def get_tensors(self):
-        return {"weight": self.weight}
+        return {self.weight_name: self.weight}
 
     def table(self):
         return self.weight

@@ -14,11 +14,12 @@ from .spec import PartSpec, TensorSpec
 @register("head", "linear_head")
 class LinearHead(Head):
     def __init__(self, *, vocab_size: int, norm: PartSpec, tied: bool, weight_prefix: str | None = "lm_head.",
-                 hidden_size: int, dtype, device):
+                 weight_name: str = "weight", hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         self.vocab_size = vocab_size
         self.wants_tie = bool(tied)
         self.weight_prefix = weight_prefix
+        self.weight_name = weight_name      # the matrix is the tensor weight_prefix + weight_name
         self.norm_prefix = norm.prefix
         self.norm = lookup("norm", norm.kind)(hidden_size=hidden_size, dtype=dtype, device=device, **norm.params)
         self.weight = None
@@ -26,7 +27,7 @@ class LinearHead(Head):
     def tensor_specs(self):
         specs = {self.norm_prefix + local: ts for local, ts in self.norm.tensor_specs().items()}
         if not self.wants_tie:
-            specs[self.weight_prefix + "weight"] = TensorSpec((self.vocab_size, self.hidden_size))
+            specs[self.weight_prefix + self.weight_name] = TensorSpec((self.vocab_size, self.hidden_size))
         return specs
 
     def set_tensors(self, tensors):
@@ -34,12 +35,12 @@ class LinearHead(Head):
         self.norm.set_tensors({name[n:]: t for name, t in tensors.items() if name.startswith(self.norm_prefix)
                                and name[n:] in self.norm.tensor_specs()})
         if not self.wants_tie:
-            self.weight = linear.Weight(tensors[self.weight_prefix + "weight"])
+            self.weight = linear.Weight(tensors[self.weight_prefix + self.weight_name])
 
     def get_tensors(self):
         out = {self.norm_prefix + local: t for local, t in self.norm.get_tensors().items()}
         if not self.wants_tie:
-            out[self.weight_prefix + "weight"] = self.weight.t
+            out[self.weight_prefix + self.weight_name] = self.weight.t
         return out
 
     def tie(self, table):

@@ -12,21 +12,28 @@ from .spec import TensorSpec
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
     """y = x * (1 / sqrt(mean(x^2) + eps)) * weight; statistics in float32.  The weight
-    multiplies directly (no 1 + w)."""
+    multiplies directly, unless `unit_offset` says that it is stored around zero: then the
+    factor is 1 + weight (formed once, in float32, when the weight arrives).  `weight_name` is
+    the tensor's name below the part's prefix."""
 
-    def __init__(self, *, eps: float, hidden_size: int, dtype, device):
+    def __init__(self, *, eps: float, unit_offset: bool = False, weight_name: str = "weight", hidden_size: int,
+                 dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         self.eps = float(eps)
-        self.weight = None
+        self.unit_offset = bool(unit_offset)
+        self.weight_name = weight_name
+        self.weight = self.factor = None
 
     def tensor_specs(self):
-        return {"weight": TensorSpec((self.hidden_size,), role="vector", init="ones")}
+        return {self.weight_name: TensorSpec((self.hidden_size,), role="vector",
+                                             init="zeros" if self.unit_offset else "ones")}
 
     def set_tensors(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.weight_name]
+        self.factor = self.weight + 1.0 if self.unit_offset else self.weight
 
     def get_tensors(self):
-        return {"weight": self.weight}
+        return {self.weight_name: self.weight}
 
     def forward(self, x, out, rows=None):
-        return ops.rmsnorm(x, self.weight, self.eps, out, rows)
+        return ops.rmsnorm(x, self.factor, self.eps, out, rows)

@@ -11,12 +11,17 @@ from .registry import register
 _STYLES = {"half": 0, "interleaved": 1}
 
 
-def rope_tables(head_dim: int, base: float, n_positions: int):
+def rope_tables(head_dim: int, base: float, n_positions: int, exact_angles: bool = False):
     """cos, sin as float32 [n_positions, head_dim/2], built the way rope.rs:47-55 does:
     exponent = 2i/dim, theta = 1/base^exponent and angle = pos*theta are 32-bit numbers
     (the power is taken in float64 and rounded once); cos and sin are taken of the 32-bit
-    angle in float64 and rounded once."""
+    angle in float64 and rounded once.  With exact_angles frequency and angle stay float64 and
+    only cos and sin are rounded."""
     half = head_dim // 2
+    if exact_angles:
+        theta = np.power(np.float64(base), -2.0 * np.arange(half, dtype=np.float64) / np.float64(head_dim))
+        angle = np.arange(n_positions, dtype=np.float64)[:, None] * theta[None, :]
+        return np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
     exponent = (2 * np.arange(half)).astype(np.float32) / np.float32(head_dim)
     theta = (1.0 / np.power(np.float64(np.float32(base)), exponent.astype(np.float64))).astype(np.float32)
     pos = np.arange(n_positions, dtype=np.float32)
@@ -30,32 +35,42 @@ def rope_tables(head_dim: int, base: float, n_positions: int):
 class RotaryEncoding(PositionEncoding):
     """Rotates every q head and every k head by the angles of the token's absolute
     position (attention.rs:78-87); v is not rotated.  style "interleaved" pairs (2i, 2i+1)
-    as rope.rs:92-96 does; "half" pairs (i, i + dim/2)."""
+    as rope.rs:92-96 does; "half" pairs (i, i + dim/2).  `rot_dims` < head_dim rotates only
+    the first rot_dims channels of every head (frequencies base^(-2i/rot_dims), pairs within
+    them) and lets the rest pass."""
 
-    def __init__(self, *, head_dim: int, base: float, style: str = "half", hidden_size: int, dtype, device):
+    def __init__(self, *, head_dim: int, base: float, style: str = "half", rot_dims: int | None = None,
+                 exact_angles: bool = False, hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         if style not in _STYLES:
             raise ValueError(f"rope style must be one of {sorted(_STYLES)}, found {style!r}")
-        if head_dim % 2:
-            raise ValueError(f"rope needs an even head_dim, found {head_dim}")
+        rot = head_dim if rot_dims is None else int(rot_dims)
+        if rot % 2 or not 0 < rot <= head_dim:
+            raise ValueError(f"rope rotates an even number of channels, at most head_dim {head_dim}; found {rot}")
         self.head_dim = head_dim
+        self.rot_dims = rot
         self.base = float(base)
         self.style = _STYLES[style]
+        self.exact_angles = bool(exact_angles)
         self.cos = self.sin = None
+
+    @property
+    def partial(self) -> bool:
+        return self.rot_dims != self.head_dim
 
     def prepare(self, max_positions: int) -> None:
         if self.cos is None or self.cos.shape[0] < max_positions:
-            cos, sin = rope_tables(self.head_dim, self.base, max_positions)
-            self.cos = torch.from_numpy(cos).to(self.device)
-            self.sin = torch.from_numpy(sin).to(self.device)
+            cos, sin = rope_tables(self.rot_dims, self.base, max_positions, self.exact_angles)
+            self.cos = torch.from_numpy(cos).contiguous().to(self.device)
+            self.sin = torch.from_numpy(sin).contiguous().to(self.device)
 
-    def apply_and_store(self, qkv, ctx, cache_layer, *, n_heads, n_kv_heads, head_dim, write_kv):
+    def apply_and_store(self, qkv, ctx, cache_layer, *, n_heads, n_kv_heads, head_dim, write_kv, v_head_dim=None):
         if self.cos is None or self.cos.shape[0] < ctx.max_len:
             raise RuntimeError("rope tables do not cover the step's positions; call prepare() first")
         ops.rope_cache_write(qkv, self.cos, self.sin, ctx.token_pos, ctx.token_seq, ctx.seq_slot,
                              ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads,
                              n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
-                             style=self.style, write_kv=write_kv)
+                             style=self.style, write_kv=write_kv, rot_dims=self.rot_dims, v_head_dim=v_head_dim)
 
     def apply_and_store_from_accumulators(self, acc, bias, q_out, ctx, cache_layer, *, n_heads, n_kv_heads,
                                           head_dim, write_kv):

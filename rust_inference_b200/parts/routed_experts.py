@@ -1,0 +1,111 @@
+"""A routed mixture of gated feed-forward experts, with an optional always-on shared expert."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import linear, ops
+from .base import FeedForward
+from .registry import register
+from .spec import TensorSpec
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """`n_experts` experts of the form down(silu(gate x) * (up x)), of which every token uses `top`.
+
+    Router: s = sigmoid(W_router x) in float32.  The choice is made on s + correction, limited to the
+    `group_keep` best of `n_groups` equal groups of neighbouring experts (a group's score is the sum of
+    its two largest choice scores; the other groups' experts count as minus infinity).  The chosen
+    experts' results are weighted by their s divided by the sum of those (+ 1e-20).  A shared expert of
+    width `shared_size` (None: none) runs for every token and is added times sigmoid(w_sg . x).
+
+    Everything from the router to the sum runs on the device (`csrc/moe.cu`), so decode steps stay
+    inside captured graphs.  Experts are kept stacked: gate, up [experts, ff, hidden], down [experts,
+    hidden, ff].  `names` gives the tensors' names below the part's prefix; "{e}" is the expert's number."""
+
+    _NAMES = {"router": "router.weight", "correction": "router.correction", "gate": "experts.{e}.gate_proj.weight",
+              "up": "experts.{e}.up_proj.weight", "down": "experts.{e}.down_proj.weight",
+              "shared_gate": "shared.gate_proj.weight", "shared_up": "shared.up_proj.weight",
+              "shared_down": "shared.down_proj.weight", "shared_mix": "shared.mix.weight"}
+
+    def __init__(self, *, n_experts: int, top: int, expert_size: int, n_groups: int = 1, group_keep: int = 1,
+                 shared_size: int | None = None, names: dict | None = None, hidden_size: int, dtype, device):
+        super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+        if not 0 < top <= n_experts:
+            raise ValueError(f"{top} of {n_experts} experts cannot be chosen")
+        if n_groups <= 0 or n_experts % n_groups or not 0 < group_keep <= n_groups:
+            raise ValueError(f"{n_experts} experts do not form {n_groups} equal groups of which {group_keep} are kept")
+        if group_keep * (n_experts // n_groups) < top:
+            raise ValueError(f"{group_keep} groups of {n_experts // n_groups} experts cannot give {top} choices")
+        self.n_experts, self.top, self.expert_size = n_experts, top, expert_size
+        self.n_groups, self.group_keep = n_groups, group_keep
+        self.shared_size = shared_size
+        self.names = dict(self._NAMES, **(names or {}))
+        self.router = self.correction = self.w_gate = self.w_up = self.w_down = None
+        self.shared = self.shared_mix = None
+
+    def tensor_specs(self):
+        h, f, nm = self.hidden_size, self.expert_size, self.names
+        specs = {nm["router"]: TensorSpec((self.n_experts, h), role="vector"),
+                 nm["correction"]: TensorSpec((self.n_experts,), role="vector", init="zeros")}
+        for e in range(self.n_experts):
+            specs[nm["gate"].format(e=e)] = TensorSpec((f, h))
+            specs[nm["up"].format(e=e)] = TensorSpec((f, h))
+            specs[nm["down"].format(e=e)] = TensorSpec((h, f))
+        if self.shared_size is not None:
+            s = self.shared_size
+            specs[nm["shared_gate"]] = TensorSpec((s, h))
+            specs[nm["shared_up"]] = TensorSpec((s, h))
+            specs[nm["shared_down"]] = TensorSpec((h, s))
+            specs[nm["shared_mix"]] = TensorSpec((1, h), role="vector")
+        return specs
+
+    def set_tensors(self, tensors):
+        nm, n = self.names, self.n_experts
+        self.router = tensors[nm["router"]].contiguous()
+        self.correction = tensors[nm["correction"]].contiguous()
+        self.w_gate = torch.stack([tensors[nm["gate"].format(e=e)] for e in range(n)]).contiguous()
+        self.w_up = torch.stack([tensors[nm["up"].format(e=e)] for e in range(n)]).contiguous()
+        self.w_down = torch.stack([tensors[nm["down"].format(e=e)] for e in range(n)]).contiguous()
+        if self.shared_size is not None:
+            self.shared = tuple(linear.Weight(tensors[nm[k]]) for k in ("shared_gate", "shared_up", "shared_down"))
+            self.shared_mix = tensors[nm["shared_mix"]].reshape(-1).contiguous()
+
+    def get_tensors(self):
+        nm = self.names
+        out = {nm["router"]: self.router, nm["correction"]: self.correction}
+        for e in range(self.n_experts):
+            out[nm["gate"].format(e=e)] = self.w_gate[e]
+            out[nm["up"].format(e=e)] = self.w_up[e]
+            out[nm["down"].format(e=e)] = self.w_down[e]
+        if self.shared_size is not None:
+            out[nm["shared_gate"]], out[nm["shared_up"]], out[nm["shared_down"]] = (w.t for w in self.shared)
+            out[nm["shared_mix"]] = self.shared_mix.view(1, -1)
+        return out
+
+    def forward(self, x, residual, ctx):
+        n, h, top, experts = x.shape[0], self.hidden_size, self.top, self.n_experts
+        pairs = n * top
+        ids = ctx.buffer("moe_ids", (n, top), torch.int32)
+        weights = ctx.buffer("moe_weights", (n, top), torch.float32)
+        gate = ctx.buffer("moe_shared_gate", (n,), torch.float32) if self.shared is not None else None
+        ops.moe_route(x, self.router, self.correction, ids, weights, top=top, groups=self.n_groups,
+                      keep=self.group_keep, gate_weight=self.shared_mix, gate_out=gate)
+        rows = ops.moe_tile_rows()
+        offsets = ctx.buffer("moe_offsets", (experts + 1,), torch.int32)
+        order = ctx.buffer("moe_order", (pairs,), torch.int32)
+        tiles = ctx.buffer("moe_tiles", (2 * (-(-pairs // rows) + experts),), torch.int32)
+        n_tiles = ctx.buffer("moe_n_tiles", (1,), torch.int32)
+        ops.moe_arrange(ids, pairs, experts, rows, offsets, order, tiles, n_tiles)
+        act = ctx.buffer("moe_act", (pairs, self.expert_size), self.dtype)
+        ops.moe_grouped_simt(x, self.w_gate, self.w_up, act, offsets, order, tiles, n_tiles, n_pairs=pairs, top=top)
+        y = ctx.buffer("moe_y", (pairs, h), torch.float32)
+        ops.moe_grouped_simt(act, self.w_down, None, y, offsets, order, tiles, n_tiles, n_pairs=pairs, top=top)
+        shared_y = None
+        if self.shared is not None:
+            w_gate, w_up, w_down = self.shared
+            sact = ctx.buffer("moe_shared_act", (n, self.shared_size), self.dtype)
+            linear.gated(x, w_gate, w_up, sact, ctx)
+            shared_y = ctx.buffer("moe_shared_y", (n, h), torch.float32)
+            linear.logits(sact, w_down, shared_y, ctx)
+        ops.moe_combine(residual, y, weights, top=top, shared_y=shared_y, gate=gate)
