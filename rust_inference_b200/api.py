@@ -46,9 +46,10 @@ class Model:
         eng = self.engine
         item = 4 if eng.dtype.itemsize == 4 else 2
         per_position = 0
-        for req in eng.model.cache_requests():
-            if req is not None and hasattr(req, "n_kv_heads"):
-                per_position += 2 * req.n_kv_heads * req.head_dim * item
+        for entry in eng.model.cache_requests():
+            for req in (entry if isinstance(entry, tuple) else (entry,)):
+                if req is not None and hasattr(req, "n_kv_heads"):
+                    per_position += req.n_kv_heads * (req.head_dim + (req.v_head_dim or req.head_dim)) * item
         return {"weight_bytes": eng.model.weight_bytes(), "weight_bytes_per_step": eng.model.weight_bytes(False),
                 "cache_bytes": eng.cache.bytes(), "cache_bytes_per_position": per_position}
 
