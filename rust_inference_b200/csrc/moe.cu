@@ -14,7 +14,10 @@
 //   combine   residual[t] += sum_c weight[t, c] * y[t * top + c] (+ gate[t] * shared[t]), in a fixed order
 //
 // A pair is p = token * top + choice; its rows of act and y sit at p, so the order of the lists
-// decides only which block works on which rows.
+// decides only which block works on which rows.  The tensor-core form of the contractions
+// (`moe_tcgen05.cu`) wants an expert's rows consecutive instead: `gather` copies the activations
+// into the order of the list, act and y stay in that order, and `combine` finds pair p's row through
+// `place`.
 #include "common.cuh"
 
 using namespace ri;
@@ -131,10 +134,10 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
 // ---- arrange ---------------------------------------------------------------------------------
 // One block.  offsets[e]..offsets[e+1] index `order`, which lists the pairs of expert e; tiles[2k],
 // tiles[2k+1] = (expert, first index into `order`) of tile k, each tile holding at most `tile_rows`
-// pairs of one expert; n_tiles[0] their number.
+// pairs of one expert; n_tiles[0] their number; place[p] (optional) the index of pair p in `order`.
 __global__ void __launch_bounds__(1024)
 moe_arrange_kernel(const int* __restrict__ ids, int n_pairs, int experts, int tile_rows, int* __restrict__ offsets,
-                   int* __restrict__ order, int* __restrict__ tiles, int* __restrict__ n_tiles) {
+                   int* __restrict__ order, int* __restrict__ tiles, int* __restrict__ n_tiles, int* __restrict__ place) {
     extern __shared__ int sh[];
     int* count = sh;                 // [experts]
     int* start = sh + experts;       // [experts + 1]
@@ -168,7 +171,24 @@ moe_arrange_kernel(const int* __restrict__ ids, int n_pairs, int experts, int ti
     // of the results, so the order changes no number
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int e = ids[p];
-        if (e >= 0 && e < experts) order[start[e] + atomicAdd(&fill[e], 1)] = p;
+        if (e >= 0 && e < experts) {
+            const int at = start[e] + atomicAdd(&fill[e], 1);
+            order[at] = p;
+            if (place != nullptr) place[p] = at;
+        }
+    }
+}
+
+// xs[i, :] = x[order[i] / top, :]: the activations in the order of the list, 16 bytes at a time
+// (width a multiple of 8 bf16).
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ order,
+                                  int n_pairs, int top, int vecs) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const size_t total = (size_t)n_pairs * vecs;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / vecs), c = (int)(i % vecs);
+        xs[i] = x[(size_t)(order[r] / top) * vecs + c];
     }
 }
 
@@ -253,15 +273,18 @@ moe_grouped_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __
 
 __global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ y,
                                    const float* __restrict__ weights, const float* __restrict__ shared_y,
-                                   const float* __restrict__ gate, int n_tokens, int width, int top) {
+                                   const float* __restrict__ gate, const int* __restrict__ place, int n_tokens, int width,
+                                   int top) {
     let_next_kernel_start();
     wait_for_previous_kernels();
     const size_t total = (size_t)n_tokens * width;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(i / width), d = (int)(i % width);
         float acc = 0.f;
-        for (int c = 0; c < top; ++c)
-            acc = fmaf(weights[(size_t)t * top + c], y[((size_t)t * top + c) * width + d], acc);
+        for (int c = 0; c < top; ++c) {
+            const size_t p = (size_t)t * top + c;
+            acc = fmaf(weights[p], y[(place != nullptr ? (size_t)place[p] : p) * width + d], acc);
+        }
         if (shared_y != nullptr) acc = fmaf(gate[t], shared_y[i], acc);
         residual[i] += acc;
     }
@@ -297,14 +320,24 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
 RI_API int ri_moe_tile_rows() { return GM; }
 
 RI_API int ri_moe_arrange(const int* ids, int n_pairs, int experts, int tile_rows, int* offsets, int* order, int* tiles,
-                          int* n_tiles, cudaStream_t stream) {
+                          int* n_tiles, int* place, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (tile_rows <= 0) return fail("moe_arrange: tile of %d rows", tile_rows);
     const size_t smem = (size_t)(3 * experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return fail("moe_arrange: %d experts exceed the kernel's shared memory", experts);
     cudaError_t e = launch_dependent(moe_arrange_kernel, 1, 1024, smem, stream, ids, n_pairs, experts, tile_rows, offsets,
-                                     order, tiles, n_tiles);
+                                     order, tiles, n_tiles, place);
     return check_launch(e, "moe_arrange");
+}
+
+RI_API int ri_moe_gather(const void* x, void* xs, const int* order, int n_pairs, int top, int width, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (width % 8 || (uintptr_t)x % 16 || (uintptr_t)xs % 16) return fail("moe_gather: rows of %d bf16 are not 16-byte runs", width);
+    const size_t total = (size_t)n_pairs * (width / 8);
+    const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
+    cudaError_t e = launch_dependent(moe_gather_kernel, blocks, 256, 0, stream, (const uint4*)x, (uint4*)xs, order, n_pairs,
+                                     top, width / 8);
+    return check_launch(e, "moe_gather");
 }
 
 // gate != 0: x [tokens, K], w / w2 [experts, N, K] -> out<dtype> [pairs, N]; else x [pairs, K], w -> out<float> [pairs, N]
@@ -326,12 +359,12 @@ RI_API int ri_moe_grouped_simt(const void* x, const void* w, const void* w2, voi
 }
 
 RI_API int ri_moe_combine(float* residual, const float* y, const float* weights, const float* shared_y, const float* gate,
-                          int n_tokens, int width, int top, cudaStream_t stream) {
+                          const int* place, int n_tokens, int width, int top, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const size_t total = (size_t)n_tokens * width;
     const int blocks = (int)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192);
     cudaError_t e = launch_dependent(moe_combine_kernel, blocks, 256, 0, stream, residual, y, weights, shared_y, gate,
-                                     n_tokens, width, top);
+                                     place, n_tokens, width, top);
     return check_launch(e, "moe_combine");
 }
 

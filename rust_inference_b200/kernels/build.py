@@ -32,6 +32,7 @@ MODULES = {
     "attention_tcgen05": "attention_tcgen05.cu",
     "recurrent": "recurrent.cu",
     "moe": "moe.cu",
+    "moe_tcgen05": "moe_tcgen05.cu",
     "wait_probe": "wait_probe.cu",
     "host_runtime": "host_runtime.cpp",
 }

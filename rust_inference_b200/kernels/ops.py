@@ -488,17 +488,28 @@ def moe_tile_rows() -> int:
 
 
 def moe_arrange(ids: torch.Tensor, n_pairs: int, experts: int, tile_rows: int, offsets: torch.Tensor,
-                order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor) -> None:
+                order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor, place: torch.Tensor | None = None) -> None:
     """The (token, choice) pairs listed expert by expert (`offsets` int32 [experts + 1] into `order` int32
     [pairs]) and cut into tiles of at most tile_rows pairs of one expert (`tiles` int32 [2 * (pairs /
-    tile_rows + experts)]: expert and first index; `n_tiles` int32 [1])."""
-    _need_cuda(ids, offsets, order, tiles, n_tiles)
-    for t in (ids, offsets, order, tiles, n_tiles):
-        _need(t.dtype == torch.int32 and t.is_contiguous(), "moe_arrange: int32 arrays")
-    _need(offsets.numel() >= experts + 1 and order.numel() >= n_pairs
+    tile_rows + experts)]: expert and first index; `n_tiles` int32 [1]).  `place` int32 [pairs]: where in
+    `order` each pair stands."""
+    _need_cuda(ids, offsets, order, tiles, n_tiles, place)
+    for t in (ids, offsets, order, tiles, n_tiles, place):
+        _need(t is None or (t.dtype == torch.int32 and t.is_contiguous()), "moe_arrange: int32 arrays")
+    _need(offsets.numel() >= experts + 1 and order.numel() >= n_pairs and (place is None or place.numel() >= n_pairs)
           and tiles.numel() >= 2 * (-(-n_pairs // tile_rows) + experts), "moe_arrange: arrays too small")
     _call("moe", "ri_moe_arrange", _p(ids), c_int(n_pairs), c_int(experts), c_int(tile_rows), _p(offsets), _p(order),
-          _p(tiles), _p(n_tiles), _stream())
+          _p(tiles), _p(n_tiles), _p(place), _stream())
+
+
+def moe_gather(x: torch.Tensor, xs: torch.Tensor, order: torch.Tensor, *, n_pairs: int, top: int) -> torch.Tensor:
+    """xs[i] = x[order[i] // top]: the activations in the order of the experts' lists (bfloat16 rows of a
+    multiple of 8 values)."""
+    _need_cuda(x, xs, order)
+    _need(x.dtype == torch.bfloat16 and xs.dtype == torch.bfloat16 and x.is_contiguous() and xs.is_contiguous()
+          and xs.shape == (n_pairs, x.shape[1]) and x.shape[0] * top >= n_pairs, "moe_gather: shapes")
+    _call("moe", "ri_moe_gather", _p(x), _p(xs), _p(order), c_int(n_pairs), c_int(top), c_int(x.shape[1]), _stream())
+    return xs
 
 
 def moe_grouped_simt(x: torch.Tensor, w: torch.Tensor, w2: torch.Tensor | None, out: torch.Tensor, offsets, order,
@@ -521,14 +532,17 @@ def moe_grouped_simt(x: torch.Tensor, w: torch.Tensor, w2: torch.Tensor | None, 
 
 
 def moe_combine(residual: torch.Tensor, y: torch.Tensor, weights: torch.Tensor, *, top: int,
-                shared_y: torch.Tensor | None = None, gate: torch.Tensor | None = None) -> None:
-    """residual[t] += sum_c weights[t, c] * y[t * top + c] (+ gate[t] * shared_y[t]); all float32."""
-    _need_cuda(residual, y, weights, shared_y, gate)
+                shared_y: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                place: torch.Tensor | None = None) -> None:
+    """residual[t] += sum_c weights[t, c] * y[row of pair t * top + c] (+ gate[t] * shared_y[t]); all float32.
+    A pair's row of y is the pair's own number, or place[pair] when `place` is given."""
+    _need_cuda(residual, y, weights, shared_y, gate, place)
     n, width = residual.shape
     for t in (residual, y, weights, shared_y, gate):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "moe_combine: float32 tensors")
     _need(y.shape == (n * top, width) and weights.numel() >= n * top, "moe_combine: shapes")
+    _need(place is None or (place.dtype == torch.int32 and place.numel() >= n * top), "moe_combine: place must be int32 [pairs]")
     _need((shared_y is None) == (gate is None) and (shared_y is None or (shared_y.shape == (n, width) and gate.numel() >= n)),
           "moe_combine: the shared result and its gate go together")
-    _call("moe", "ri_moe_combine", _p(residual), _p(y), _p(weights), _p(shared_y), _p(gate), c_int(n), c_int(width),
-          c_int(top), _stream())
+    _call("moe", "ri_moe_combine", _p(residual), _p(y), _p(weights), _p(shared_y), _p(gate), _p(place), c_int(n),
+          c_int(width), c_int(top), _stream())

@@ -25,6 +25,10 @@ STATUS_TEXT = {
     21: "decode attention: the TMA producer waited too long for a free stage",
     22: "decode attention: a compute warp waited too long for a page",
     24: "decode attention: a TMA load did not land before the CTA had to leave",
+    31: "experts: the TMA producer waited too long for a free stage",
+    32: "experts: the MMA issuer waited too long for a TMA load",
+    33: "experts: the epilogue waited too long for the accumulator",
+    34: "experts: a TMA load did not land before the CTA had to leave",
 }
 
 
@@ -136,4 +140,45 @@ def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, 
     _call("gemm_tcgen05", "ri_gemm_tcgen05", c_void_p(map_x.data_ptr()), c_void_p(weight_map(w).data_ptr()),
           c_void_p(map_w2.data_ptr() if map_w2 is not None else 0), _p(bias), _p(out), c_int(mode), c_int(m),
           c_int(n), c_int(k), c_int(split_k), c_void_p(st.data_ptr()), _stream())
+    return out
+
+
+# ---- the experts' grouped contractions (csrc/moe_tcgen05.cu) ---------------------------------------
+GROUPED_TILE_ROWS = 128
+
+
+def grouped_supports(x_dtype: torch.dtype, w: torch.Tensor) -> bool:
+    """bf16, and K a multiple of 8 (16-byte rows for TMA)."""
+    return x_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[2] % 8 == 0 and w.shape[2] >= 8
+
+
+_stacked_maps: dict = {}
+
+
+def _stacked_map(w: torch.Tensor) -> torch.Tensor:
+    """The tensor map of a stack of matrices [experts, N, K] seen as one [experts * N, K] matrix."""
+    key = (w.data_ptr(), tuple(w.shape))
+    m = _stacked_maps.get(key)
+    if m is None:
+        m = _stacked_maps[key] = _encode(w, w.shape[0] * w.shape[1], w.shape[2], 128)
+    return m
+
+
+def grouped_gemm(x: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets, tiles, n_tiles, *, n_pairs: int):
+    """For every expert e the rows offsets[e]..offsets[e+1] of x [pairs, K] times w[e]^T ([experts, N, K]):
+    with w2 out<bf16> = silu(x w[e]^T) * (x w2[e]^T), without out<float32> = x w[e]^T.  `tiles` / `n_tiles` are
+    the arrange kernel's for tiles of GROUPED_TILE_ROWS rows."""
+    _need_cuda(x, w, w2, out, offsets, tiles, n_tiles)
+    experts, n, k = w.shape
+    gate = w2 is not None
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+          and x.shape == (n_pairs, k), "grouped_gemm: x must be bf16 [pairs, K]")
+    _need(not gate or (w2.shape == w.shape and w2.dtype == torch.bfloat16 and w2.is_contiguous()), "grouped_gemm: second matrix")
+    _need(out.is_contiguous() and out.shape == (n_pairs, n) and out.dtype == (torch.bfloat16 if gate else torch.float32),
+          "grouped_gemm: out")
+    map_x = _x_map(x, 128)
+    st = status_word()
+    _call("moe_tcgen05", "ri_moe_grouped_tcgen05", c_void_p(map_x.data_ptr()), c_void_p(_stacked_map(w).data_ptr()),
+          c_void_p(_stacked_map(w2).data_ptr() if gate else 0), _p(out), c_int(1 if gate else 0), _p(offsets), _p(tiles),
+          _p(n_tiles), c_int(n_pairs), c_int(experts), c_int(n), c_int(k), c_void_p(st.data_ptr()), _stream())
     return out

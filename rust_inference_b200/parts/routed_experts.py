@@ -83,6 +83,17 @@ class RoutedExperts(FeedForward):
             out[nm["shared_mix"]] = self.shared_mix.view(1, -1)
         return out
 
+    # steps of more tokens than this run the experts' products on the tensor cores (tiles of 128 rows of one
+    # expert); smaller ones are bound by the chosen experts' weights, which the FFMA form streams in tiles of 32
+    TENSOR_CORE_MIN_TOKENS = 16
+
+    def _on_tensor_cores(self, x) -> bool:
+        if x.dtype != torch.bfloat16 or x.shape[0] <= self.TENSOR_CORE_MIN_TOKENS:
+            return False
+        from ..kernels import tcgen05
+        return (tcgen05.grouped_supports(x.dtype, self.w_gate) and tcgen05.grouped_supports(x.dtype, self.w_down)
+                and self.hidden_size % 8 == 0)
+
     def forward(self, x, residual, ctx):
         n, h, top, experts = x.shape[0], self.hidden_size, self.top, self.n_experts
         pairs = n * top
@@ -91,16 +102,29 @@ class RoutedExperts(FeedForward):
         gate = ctx.buffer("moe_shared_gate", (n,), torch.float32) if self.shared is not None else None
         ops.moe_route(x, self.router, self.correction, ids, weights, top=top, groups=self.n_groups,
                       keep=self.group_keep, gate_weight=self.shared_mix, gate_out=gate)
-        rows = ops.moe_tile_rows()
+        fast = self._on_tensor_cores(x)
+        if fast:
+            from ..kernels import tcgen05
+            rows = tcgen05.GROUPED_TILE_ROWS
+        else:
+            rows = ops.moe_tile_rows()
         offsets = ctx.buffer("moe_offsets", (experts + 1,), torch.int32)
         order = ctx.buffer("moe_order", (pairs,), torch.int32)
         tiles = ctx.buffer("moe_tiles", (2 * (-(-pairs // rows) + experts),), torch.int32)
         n_tiles = ctx.buffer("moe_n_tiles", (1,), torch.int32)
-        ops.moe_arrange(ids, pairs, experts, rows, offsets, order, tiles, n_tiles)
+        place = ctx.buffer("moe_place", (pairs,), torch.int32) if fast else None
+        ops.moe_arrange(ids, pairs, experts, rows, offsets, order, tiles, n_tiles, place)
         act = ctx.buffer("moe_act", (pairs, self.expert_size), self.dtype)
-        ops.moe_grouped_simt(x, self.w_gate, self.w_up, act, offsets, order, tiles, n_tiles, n_pairs=pairs, top=top)
         y = ctx.buffer("moe_y", (pairs, h), torch.float32)
-        ops.moe_grouped_simt(act, self.w_down, None, y, offsets, order, tiles, n_tiles, n_pairs=pairs, top=top)
+        if fast:
+            # an expert's rows consecutive: gather the activations into the lists' order; act and y stay in it
+            xs = ctx.buffer("moe_x_sorted", (pairs, h), self.dtype)
+            ops.moe_gather(x, xs, order, n_pairs=pairs, top=top)
+            tcgen05.grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, n_tiles, n_pairs=pairs)
+            tcgen05.grouped_gemm(act, self.w_down, None, y, offsets, tiles, n_tiles, n_pairs=pairs)
+        else:
+            ops.moe_grouped_simt(x, self.w_gate, self.w_up, act, offsets, order, tiles, n_tiles, n_pairs=pairs, top=top)
+            ops.moe_grouped_simt(act, self.w_down, None, y, offsets, order, tiles, n_tiles, n_pairs=pairs, top=top)
         shared_y = None
         if self.shared is not None:
             w_gate, w_up, w_down = self.shared
@@ -108,4 +132,4 @@ class RoutedExperts(FeedForward):
             linear.gated(x, w_gate, w_up, sact, ctx)
             shared_y = ctx.buffer("moe_shared_y", (n, h), torch.float32)
             linear.logits(sact, w_down, shared_y, ctx)
-        ops.moe_combine(residual, y, weights, top=top, shared_y=shared_y, gate=gate)
+        ops.moe_combine(residual, y, weights, top=top, shared_y=shared_y, gate=gate, place=place)

@@ -99,6 +99,49 @@ def test_grouped_expert_products(dtype, experts, top, ff, width, n):
     assert rel_err(residual, want) < (1e-5 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("experts,top,ff,width,n", [(6, 2, 24, 72, 50), (5, 1, 200, 128, 3), (12, 3, 136, 320, 700), (4, 4, 264, 64, 300)])
+def test_grouped_expert_products_on_tensor_cores(experts, top, ff, width, n):
+    """The tcgen05 form: activations gathered into the experts' order, tiles of 128 rows of one expert (an
+    expert with several tiles, experts with none, features that are not a multiple of the tile), results
+    found again through `place`."""
+    from rust_inference_b200.kernels import ops, tcgen05
+    g = torch.Generator().manual_seed(n + ff)
+    bf = torch.bfloat16
+    x = torch.randn(n, width, generator=g).to(bf)
+    wg = (torch.randn(experts, ff, width, generator=g) / math.sqrt(width)).to(bf)
+    wu = (torch.randn(experts, ff, width, generator=g) / math.sqrt(width)).to(bf)
+    wd = (torch.randn(experts, width, ff, generator=g) / math.sqrt(ff)).to(bf)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(n)]).int()
+    if n > 100 and top < experts:
+        ids[: n // 2] = ids[0]               # a few experts with many rows, the others with few or none
+    wts = torch.rand(n, top, generator=g)
+    pairs, rows = n * top, tcgen05.GROUPED_TILE_ROWS
+    i32 = lambda k: torch.zeros(k, dtype=torch.int32, device=DEV)
+    offsets, order, tiles, n_tiles, place = i32(experts + 1), i32(pairs), i32(2 * (-(-pairs // rows) + experts)), i32(1), i32(pairs)
+    ops.moe_arrange(d(ids), pairs, experts, rows, offsets, order, tiles, n_tiles, place)
+    assert torch.equal(order[place.long()].cpu(), torch.arange(pairs, dtype=torch.int32))
+    wg_d, wu_d, wd_d = d(wg), d(wu), d(wd)
+    xs = torch.empty(pairs, width, dtype=bf, device=DEV)
+    ops.moe_gather(d(x), xs, order, n_pairs=pairs, top=top)
+    assert torch.equal(xs.cpu(), x[(order.cpu().long() // top)])
+    act = torch.full((pairs, ff), float("nan"), dtype=bf, device=DEV)
+    tcgen05.grouped_gemm(xs, wg_d, wu_d, act, offsets, tiles, n_tiles, n_pairs=pairs)
+    y = torch.full((pairs, width), float("nan"), dtype=torch.float32, device=DEV)
+    tcgen05.grouped_gemm(act, wd_d, None, y, offsets, tiles, n_tiles, n_pairs=pairs)
+    residual = torch.ones(n, width, dtype=torch.float32, device=DEV)
+    ops.moe_combine(residual, y, d(wts), top=top, place=place)
+    torch.cuda.synchronize()
+    tcgen05.check_status()
+    want = torch.ones(n, width, dtype=torch.float64)
+    xd = x.double()
+    for e in range(experts):
+        a = (torch.nn.functional.silu(xd @ wg[e].double().T) * (xd @ wu[e].double().T)).to(bf).double() @ wd[e].double().T
+        for c in range(top):
+            hit = ids[:, c] == e
+            want[hit] += wts[hit, c].double()[:, None] * a[hit]
+    assert rel_err(residual, want) < 2e-2
+
+
 @pytest.mark.parametrize("heads,dim,vdim", [(2, 48, 32), (1, 72, 33), (3, 24, 40), (2, 8, 16), (1, 130, 70), (1, 300, 8)])
 def test_recurrence_in_portions_and_slots(heads, dim, vdim):
     """The recurrence kernel over a whole sequence, and cut into portions of 1, 2 and 5 tokens with the
