@@ -2,6 +2,7 @@
 """Decode and prefill throughput of the library on one B200, with rooflines.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --arch lulisun [--arch-sizes 1k|2k|4k]     (another model beside the dense decoder; see below)
 
 Default run: a Qwen2.5-7B-sized dense decoder (28 layers, hidden 3584, 28 heads, 4 kv
 heads, head_dim 128, intermediate 18944, vocabulary 152064, q/k/v biases, untied head)
@@ -26,6 +27,11 @@ in 128..2048, in a cache of 8,192 positions per sequence.  A step is one decode 
 The prompts' prefill runs the GPU into its power cap, and for some tens of milliseconds afterwards
 decode steps take up to a tenth longer.  Every decode measurement therefore runs SETTLE_STEPS untimed
 decode steps after its prefill, then the W warm-up steps, then the K timed ones.
+
+`--arch lulisun` leaves this workload alone and prints another line instead: prefill and decode
+throughput of a Lulisun-style model (chunked attention beside a gated linear recurrence, routed experts)
+and of a dense decoder of equal size, with every heavy kernel of both timed alone against its roofline
+(`rust_inference_b200/kernels/arch_bench.py`).
 
 Prints ONE JSON line.  Only one GPU is used: for --gpus > 1 it says so and exits with 2.
 """
@@ -185,6 +191,10 @@ def main() -> int:
     ap.add_argument("--tokens", type=int, default=8, help="with --kernel: tokens in the step")
     ap.add_argument("--context", type=int, default=1024, help="with --kernel: cached positions per sequence")
     ap.add_argument("--once", action="store_true", help="with --kernel: launch the workload once, untimed (for ncu)")
+    ap.add_argument("--arch", default="dense", choices=["dense", "lulisun"],
+                    help="lulisun: prefill and decode throughput of a Lulisun-style model beside a dense decoder of equal "
+                         "size, kernel by kernel against the rooflines, instead of the default workload")
+    ap.add_argument("--arch-sizes", default="2k", choices=["1k", "2k", "4k"], help="with --arch lulisun: the layer sizes")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -199,6 +209,12 @@ def main() -> int:
     if args.kernel:
         from rust_inference_b200.kernels import microbench
         return microbench.main(args.kernel, OTHER_SIZES[args.sizes], args.tokens, args.context, args.once)
+    if args.arch == "lulisun":
+        from rust_inference_b200.kernels import arch_bench
+        peaks, peak_source = load_peaks()
+        return arch_bench.main(args.arch_sizes, peaks, peak_source, prefill_tokens=max(1, args.prefill_tokens),
+                               batch=args.batch, context=args.context if args.context != 1024 else None,
+                               steps=max(1, min(args.steps, 64)))
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 

@@ -26,7 +26,8 @@
 //  attn_prefill  any number of new tokens per sequence (whole prompts, or a continuation).
 //                A CTA serves 64 consecutive query tokens of one head; the warps take 16
 //                query rows each and walk the key pages up to the causal limit: the token
-//                at position p sees keys 0..p (window > 0: p-window+1..p).
+//                at position p sees keys 0..p (window > 0: p-window+1..p; window < 0: the keys
+//                of its own block of -window positions, common.cuh: first_visible_key).
 //
 // Keys and values are only ever read from the cache: the step's new tokens were written
 // there (after rotation) before attention runs, so prefill, continuation and decode use
@@ -351,7 +352,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bfl
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
     const int n_keys = seq_len[b];                       // counts the new token, whose key is in the cache by then
     const int token = cu_seqlens[b];
-    const int first_key = (window > 0 && n_keys - window > 0) ? n_keys - window : 0;
+    const int first_key = first_visible_key(n_keys - 1, window);      // `window` is a span: > 0 the last keys, < 0 the query's block
     const int* pages = page_table + (size_t)seq_slot[b] * max_pages;
 
     const int pg_lo = first_key / PAGE, pg_hi = (n_keys + PAGE - 1) / PAGE;    // pages [pg_lo, pg_hi)
@@ -533,7 +534,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // the kernel before this one still runs.  q and the sequence's last page wait for it.
     const int n_keys = seq_len[b];
     const int token = cu_seqlens[b];
-    const int first_key = (window > 0 && n_keys - window > 0) ? n_keys - window : 0;
+    const int first_key = first_visible_key(n_keys - 1, window);      // `window` is a span: > 0 the last keys, < 0 the query's block
     const int pg_lo = first_key / PAGE, pg_hi = (n_keys + PAGE - 1) / PAGE;
     const int per = (pg_hi - pg_lo + n_splits - 1) / n_splits;
     const int pg_begin = pg_lo + split * per, pg_end = min(pg_hi, pg_begin + per);
@@ -711,7 +712,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
 
     // positions of the CTA's first and last query
     const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
-    const int first_key = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+    const int first_key = first_visible_key(pos_lo, window);
     const int pg_begin = first_key / PAGE, pg_end = pos_hi / PAGE + 1;
 
     for (int idx = threadIdx.x; idx < 64 * (HD / 8); idx += THREADS) {
@@ -760,9 +761,9 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
         const uint32_t ktile = kv_base + (2 * buf) * TILE, vtile = ktile + TILE;
         const int key_lo = pg * PAGE;
         // the warp skips pages none of its rows can see
-        const bool any = key_lo <= warp_pos_hi && (window <= 0 || key_lo + PAGE - 1 > warp_pos_lo - window);
+        const bool any = key_lo <= warp_pos_hi && key_lo + PAGE - 1 >= first_visible_key(warp_pos_lo, window);
         if (any) {
-            const bool full = key_lo + PAGE - 1 <= warp_pos_lo && (window <= 0 || key_lo > warp_pos_hi - window);
+            const bool full = key_lo + PAGE - 1 <= warp_pos_lo && key_lo >= first_visible_key(warp_pos_hi, window);
 #pragma unroll
             for (int kb = 0; kb < PAGE / 16; ++kb) {
                 float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -773,7 +774,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_ld, const __nv_bf
                     for (int e = 0; e < 4; ++e) {
                         const int key = key_lo + kb * 16 + t * 8 + 2 * tq + (e & 1);
                         const int pos = (e & 2) ? p1 : p0;
-                        const bool vis = full || (key <= pos && (window <= 0 || key > pos - window));
+                        const bool vis = full || (key <= pos && key >= first_visible_key(pos, window));
                         s[t][e] = vis ? s[t][e] * scale : -INFINITY;
                     }
                 softmax_update<2, HD / 8>(s, m, l, o);

@@ -89,7 +89,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table, int max_pages,
                        const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                        const int* __restrict__ cu_seqlens, int n_heads, int n_kv_heads, float scale_log2, int window,
-                       __nv_bfloat16* __restrict__ out, int out_ld, uint32_t smem_bytes, int* status) {
+                       float out_scale, __nv_bfloat16* __restrict__ out, int out_ld, uint32_t smem_bytes, int* status) {
     constexpr int ATOMS = HD / 64;                       // 64-wide (128-byte) column tiles per row of head_dim
     constexpr int Q_BYTES = ATOMS * BM * 128;            // [atom][128 queries][64]
     constexpr int K_BYTES = ATOMS * BN * 128;            // one buffer: [atom][64 keys][64]
@@ -121,7 +121,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int start = seq_start[b];
     const int rows = min(BM, n_new - q0);
     const int pos_lo = start + q0, pos_hi = start + q0 + rows - 1;
-    const int first_key = (window > 0 && pos_lo - window + 1 > 0) ? pos_lo - window + 1 : 0;
+    // `window` is a span (common.cuh: first_visible_key): > 0 the last keys, < 0 the query's own block of positions
+    const int first_key = first_visible_key(pos_lo, window);
     const int pg_begin = first_key / BN, n_pages = pos_hi / BN + 1 - pg_begin;
 
     const uint32_t raw = smem_u32(smem_raw);
@@ -249,6 +250,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int lane_base = (warp & 3) * 32;
         const int r = lane_base + lane;                       // row of the tile = TMEM lane
         const int pos = start + q0 + r;
+        const int first_vis = first_visible_key(pos, window);
         const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16);
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
@@ -268,7 +270,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // are folded into one multiply-add per score: p = 2^(s * scale_log2 - m).
             float mx_raw = -INFINITY;
             // pages that every row of the warp sees whole need no mask
-            const bool whole = key0 + BN - 1 <= pos_lo + lane_base && (window <= 0 || key0 > pos_lo + lane_base + 31 - window);
+            const bool whole = key0 + BN - 1 <= pos_lo + lane_base && key0 >= first_visible_key(pos_lo + lane_base + 31, window);
             if (whole) {
 #pragma unroll
                 for (int c = 0; c < BN; c += 2)
@@ -277,7 +279,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int key = key0 + c;
-                    const bool vis = key <= pos && (window <= 0 || key > pos - window);
+                    const bool vis = key <= pos && key >= first_vis;
                     if (!vis) sv[c] = 0xff800000u;              // -inf
                     mx_raw = fmaxf(mx_raw, __uint_as_float(sv[c]));
                 }
@@ -342,7 +344,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         tc_fence_after();
         if (ok && !abort_flag) {
             wait_for_previous_kernels();          // `out` must not be written while an earlier kernel may read it
-            const float inv = 1.0f / l;
+            const float inv = out_scale / l;
             __nv_bfloat16* dst = out + (size_t)(tok0 + q0 + r) * out_ld + (size_t)h * HD;
 #pragma unroll 1
             for (int c = 0; c < HD; c += 16) {
@@ -377,7 +379,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const int* page_table, int max_pages,
            const int* seq_slot, const int* seq_start, const int* cu_seqlens, int n_seqs, int max_new, int n_heads,
-           int n_kv_heads, float scale, int window, void* out, int out_ld, int* status, cudaStream_t stream) {
+           int n_kv_heads, float scale, int window, float out_scale, void* out, int out_ld, int* status, cudaStream_t stream) {
     constexpr int ATOMS = HD / 64;
     // Q, two K and two V pages, P, the barriers; with head_dim 128 no room for alignment padding is left if
     // two CTAs are to share an SM (the kernel refuses, with a status code, a shared window that needs any)
@@ -392,7 +394,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), (size_t)SMEM, stream, mq, mk, mv, page_table, max_pages,
                                      seq_slot, seq_start, cu_seqlens, n_heads, n_kv_heads, scale_log2, window,
-                                     (__nv_bfloat16*)out, out_ld, (uint32_t)SMEM, status);
+                                     out_scale, (__nv_bfloat16*)out, out_ld, (uint32_t)SMEM, status);
     return check_launch(e, "attention_tcgen05");
 }
 
@@ -420,7 +422,7 @@ RI_API int ri_attention_tcgen05_prefill(const void* map_q, const void* map_k, co
                                         int max_pages, const int* seq_slot, const int* seq_start,
                                         const int* cu_seqlens, void* out, int out_ld, int n_seqs, int max_new,
                                         int n_heads, int n_kv_heads, int hd, int page_size, float scale, int window,
-                                        int* status, cudaStream_t stream) {
+                                        float out_scale, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (!ri_attention_tcgen05_supports(hd, page_size, n_heads, n_kv_heads, 8, out_ld))
         return fail("attention_tcgen05: head_dim %d, pages of %d, %d heads over %d kv heads, out rows of %d are not supported",
@@ -432,9 +434,9 @@ RI_API int ri_attention_tcgen05_prefill(const void* map_q, const void* map_k, co
     const CUtensorMap& mv = *reinterpret_cast<const CUtensorMap*>(map_v);
     if (hd == 64)
         return launch<64>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
-                          n_kv_heads, scale, window, out, out_ld, status, stream);
+                          n_kv_heads, scale, window, out_scale, out, out_ld, status, stream);
     return launch<128>(mq, mk, mv, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads,
-                       n_kv_heads, scale, window, out, out_ld, status, stream);
+                       n_kv_heads, scale, window, out_scale, out, out_ld, status, stream);
 }
 
 RI_DEFINE_LAST_ERROR()

@@ -91,6 +91,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// Which keys a query at position `pos` sees besides causality, as one number `span`: 0: all keys 0..pos;
+// > 0: the last `span` keys; < 0: the keys of its own block of -span positions, blocks counted from
+// position 0 of the sequence.  The first visible key:
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int span) {
+    if (span > 0) return pos - span + 1 > 0 ? pos - span + 1 : 0;
+    if (span < 0) return pos - pos % (-span);
+    return 0;
+}
+
 // The reference's SiLU, stable on both sides (math.rs:137-146).
 __device__ __forceinline__ float silu_f32(float x) {
     if (x >= 0.f) {

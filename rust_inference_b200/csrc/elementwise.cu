@@ -701,6 +701,28 @@ RI_API int ri_advance_decode(int* token_pos, int* seq_start, int* seq_len, int n
     return check_launch(e, "advance_decode");
 }
 
+namespace {
+template <typename T>
+__global__ void scale_kernel(T* __restrict__ x, size_t n, float factor) {
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = from_f32<T>(to_f32<T>(x[i]) * factor);
+}
+}  // namespace
+
+// x *= factor, in place.
+RI_API int ri_scale(void* x, int dtype, long long n, float factor, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    cudaError_t e;
+    if (dtype == RI_F32) e = launch_dependent(scale_kernel<float>, blocks, 256, 0, stream, (float*)x, (size_t)n, factor);
+    else if (dtype == RI_BF16)
+        e = launch_dependent(scale_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)x, (size_t)n, factor);
+    else return fail("scale: unknown dtype %d", dtype);
+    return check_launch(e, "scale");
+}
+
 RI_API int ri_silu_mul(const void* gu, void* out, int dtype, int n_tokens, int inter, cudaStream_t stream) {
     const size_t total = (size_t)n_tokens * inter;
     if (total == 0) return 0;

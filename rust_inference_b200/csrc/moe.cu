@@ -13,6 +13,11 @@
 //             act[p] = silu(Wg[e] h) * (Wu[e] h) and y[p] = Wd[e] act[p] for pair p of expert e
 //   combine   residual[t] += sum_c weight[t, c] * y[t * top + c] (+ gate[t] * shared[t]), in a fixed order
 //
+// Every kernel here runs behind others of the same step and may come onto the SMs before they have
+// finished (programmatic dependent launch): what an earlier kernel of the step wrote is read after
+// `wait_for_previous_kernels()` through plain pointers, never `const __restrict__` ones, whose loads the
+// compiler may move ahead of the wait.
+//
 // A pair is p = token * top + choice; its rows of act and y sit at p, so the order of the lists
 // decides only which block works on which rows.  The tensor-core form of the contractions
 // (`moe_tcgen05.cu`) wants an expert's rows consecutive instead: `gather` copies the activations
@@ -40,43 +45,84 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
+constexpr int ROUTE_TOKENS = 4;           // most tokens a block routes: the router's rows are read once for all of them
 
-// One warp per token.  Shared memory per warp: score[E], choice[E], group score[G].
-template <typename T>
+template <typename T> __device__ __forceinline__ void load4_f32(const T* p, float* o);
+template <> __device__ __forceinline__ void load4_f32<float>(const float* p, float* o) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4_f32<__nv_bfloat16>(const __nv_bfloat16* p, float* o) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+
+// A block routes `per_block` tokens (1..ROUTE_TOKENS).  First its warps share out the router's rows (and
+// the shared expert's gate row): a row is read once and multiplied with every token of the block, four
+// values at a time with as many independent sums as tokens.  Then warp k makes token k's choice.
+// Shared memory per token: score[E], choice[E], group score[G].
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+moe_route_kernel(const T* x, const float* __restrict__ router, const float* __restrict__ correction,
                  const float* __restrict__ gate_w, int* __restrict__ ids, float* __restrict__ weights,
-                 float* __restrict__ gate_out, int n_tokens, int width, int experts, int top, int groups, int keep) {
+                 float* __restrict__ gate_out, int n_tokens, int width, int experts, int top, int groups, int keep,
+                 int per_block) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float* score = smem + (size_t)warp * (2 * experts + groups);
-    float* choice = score + experts;
-    float* gscore = choice + experts;
+    const int stride = 2 * experts + groups;
     let_next_kernel_start();
     wait_for_previous_kernels();
-    const int t = blockIdx.x * ROUTE_WARPS + warp;
-    if (t >= n_tokens) return;
-    const T* h = x + (size_t)t * width;
+    const int tok0 = blockIdx.x * per_block;
+    const int n_here = min(per_block, n_tokens - tok0);
 
-    for (int e = 0; e < experts; ++e) {
-        const float* w = router + (size_t)e * width;
-        float acc = 0.f;
-        for (int d = lane; d < width; d += 32) acc = fmaf(to_f32<T>(h[d]), w[d], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            const float s = sigmoid_f32(acc);
-            score[e] = s;
-            choice[e] = s + correction[e];
+    for (int e = warp; e < experts + (gate_w != nullptr ? 1 : 0); e += ROUTE_WARPS) {
+        const float* w = e < experts ? router + (size_t)e * width : gate_w;
+        float acc[ROUTE_TOKENS];
+#pragma unroll
+        for (int k = 0; k < ROUTE_TOKENS; ++k) acc[k] = 0.f;
+        if (VEC) {
+            for (int d = lane * 4; d < width; d += 128) {
+                const float4 w4 = *reinterpret_cast<const float4*>(w + d);
+#pragma unroll
+                for (int k = 0; k < ROUTE_TOKENS; ++k)
+                    if (k < n_here) {
+                        float xv[4];
+                        load4_f32<T>(x + (size_t)(tok0 + k) * width + d, xv);
+                        acc[k] = fmaf(xv[0], w4.x, fmaf(xv[1], w4.y, fmaf(xv[2], w4.z, fmaf(xv[3], w4.w, acc[k]))));
+                    }
+            }
+        } else {
+            for (int d = lane; d < width; d += 32) {
+                const float wv = w[d];
+#pragma unroll
+                for (int k = 0; k < ROUTE_TOKENS; ++k)
+                    if (k < n_here) acc[k] = fmaf(to_f32<T>(x[(size_t)(tok0 + k) * width + d]), wv, acc[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < ROUTE_TOKENS; ++k) {
+            if (k >= n_here) break;
+            const float a = warp_sum(acc[k]);
+            if (lane == 0) {
+                const float s = sigmoid_f32(a);
+                if (e < experts) {
+                    smem[k * stride + e] = s;
+                    smem[k * stride + experts + e] = s + correction[e];
+                } else {
+                    gate_out[tok0 + k] = s;
+                }
+            }
         }
     }
-    if (gate_w != nullptr) {
-        float acc = 0.f;
-        for (int d = lane; d < width; d += 32) acc = fmaf(to_f32<T>(h[d]), gate_w[d], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) gate_out[t] = sigmoid_f32(acc);
-    }
-    __syncwarp();
+    __syncthreads();
+    if (warp >= n_here) return;
+    const int t = tok0 + warp;
+    float* score = smem + (size_t)warp * stride;
+    float* choice = score + experts;
+    float* gscore = choice + experts;
 
     // groups: the sum of a group's two largest choice scores; all but the `keep` best are shut out
     const int size = experts / groups;
@@ -136,7 +182,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
 // tiles[2k+1] = (expert, first index into `order`) of tile k, each tile holding at most `tile_rows`
 // pairs of one expert; n_tiles[0] their number; place[p] (optional) the index of pair p in `order`.
 __global__ void __launch_bounds__(1024)
-moe_arrange_kernel(const int* __restrict__ ids, int n_pairs, int experts, int tile_rows, int* __restrict__ offsets,
+moe_arrange_kernel(const int* ids, int n_pairs, int experts, int tile_rows, int* __restrict__ offsets,
                    int* __restrict__ order, int* __restrict__ tiles, int* __restrict__ n_tiles, int* __restrict__ place) {
     extern __shared__ int sh[];
     int* count = sh;                 // [experts]
@@ -181,7 +227,7 @@ moe_arrange_kernel(const int* __restrict__ ids, int n_pairs, int experts, int ti
 
 // xs[i, :] = x[order[i] / top, :]: the activations in the order of the list, 16 bytes at a time
 // (width a multiple of 8 bf16).
-__global__ void moe_gather_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ order,
+__global__ void moe_gather_kernel(const uint4* x, uint4* __restrict__ xs, const int* order,
                                   int n_pairs, int top, int vecs) {
     let_next_kernel_start();
     wait_for_previous_kernels();
@@ -199,16 +245,15 @@ constexpr int GM = 32, GN = 64, GK = 16, G_THREADS = 256;      // a tile of 32 p
 // else: y[p, n]   = sum_k Wd[e][n, k] act[p, k]                                                  (float out)
 template <typename T, bool GATE>
 __global__ void __launch_bounds__(G_THREADS)
-moe_grouped_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __restrict__ W2, void* __restrict__ out_,
-                   const int* __restrict__ offsets, const int* __restrict__ order, const int* __restrict__ tiles,
-                   const int* __restrict__ n_tiles, int top, int N, int K) {
+moe_grouped_kernel(const T* X, const T* __restrict__ W, const T* __restrict__ W2, void* __restrict__ out_,
+                   const int* offsets, const int* order, const int* tiles, const int* n_tiles, int top, int N, int K) {
     __shared__ float Xs[GK][GM + 1];
     __shared__ float Ws[GK][GN + 1];
     __shared__ float W2s[GATE ? GK : 1][GATE ? GN + 1 : 1];
     __shared__ int rows[GM];
     let_next_kernel_start();
     wait_for_previous_kernels();
-    if ((int)blockIdx.x >= n_tiles[0]) return;
+    if ((int)blockIdx.x >= *reinterpret_cast<const volatile int*>(n_tiles)) return;
     const int e = tiles[2 * blockIdx.x], first = tiles[2 * blockIdx.x + 1];
     const int n_rows = min(GM, offsets[e + 1] - first);
     const int n0 = blockIdx.y * GN;
@@ -271,10 +316,8 @@ moe_grouped_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __
     }
 }
 
-__global__ void moe_combine_kernel(float* __restrict__ residual, const float* __restrict__ y,
-                                   const float* __restrict__ weights, const float* __restrict__ shared_y,
-                                   const float* __restrict__ gate, const int* __restrict__ place, int n_tokens, int width,
-                                   int top) {
+__global__ void moe_combine_kernel(float* residual, const float* y, const float* weights, const float* shared_y,
+                                   const float* gate, const int* place, int n_tokens, int width, int top) {
     let_next_kernel_start();
     wait_for_previous_kernels();
     const size_t total = (size_t)n_tokens * width;
@@ -301,19 +344,21 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
         return fail("moe_route: %d experts in %d groups, %d kept", experts, groups, keep);
     if ((long long)keep * (experts / groups) < top)
         return fail("moe_route: %d groups of %d experts cannot give %d choices", keep, experts / groups, top);
-    const size_t smem = (size_t)ROUTE_WARPS * (2 * experts + groups) * sizeof(float);
+    // few tokens: one per block, so that the router's rows are shared out over more SMs
+    const int per_block = n_tokens >= 4 * 148 * ROUTE_TOKENS ? ROUTE_TOKENS : (n_tokens >= 2 * 148 ? 2 : 1);
+    const size_t smem = (size_t)per_block * (2 * experts + groups) * sizeof(float);
     if (smem > 48 * 1024) return fail("moe_route: %d experts exceed the router kernel's shared memory", experts);
-    const int blocks = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    const int blocks = (n_tokens + per_block - 1) / per_block;
+    const bool vec = width % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)router % 16 == 0 &&
+                     (gate_w == nullptr || (uintptr_t)gate_w % 16 == 0);
     cudaError_t e;
-    if (dtype == RI_F32)
-        e = launch_dependent(moe_route_kernel<float>, blocks, ROUTE_WARPS * 32, smem, stream, (const float*)x, router,
-                             correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top, groups, keep);
-    else if (dtype == RI_BF16)
-        e = launch_dependent(moe_route_kernel<__nv_bfloat16>, blocks, ROUTE_WARPS * 32, smem, stream,
-                             (const __nv_bfloat16*)x, router, correction, gate_w, ids, weights, gate_out, n_tokens, width,
-                             experts, top, groups, keep);
-    else
-        return fail("moe_route: unknown dtype %d", dtype);
+#define RI_ROUTE(T, V) launch_dependent(moe_route_kernel<T, V>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)x, router, \
+                                        correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top, groups, keep, \
+                                        per_block)
+    if (dtype == RI_F32) e = vec ? RI_ROUTE(float, true) : RI_ROUTE(float, false);
+    else if (dtype == RI_BF16) e = vec ? RI_ROUTE(__nv_bfloat16, true) : RI_ROUTE(__nv_bfloat16, false);
+    else return fail("moe_route: unknown dtype %d", dtype);
+#undef RI_ROUTE
     return check_launch(e, "moe_route");
 }
 

@@ -90,8 +90,8 @@ __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, 
 template <bool GATE>
 __global__ void __launch_bounds__(THREADS, 1)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
-                      const __grid_constant__ CUtensorMap map_x, void* __restrict__ out_, const int* __restrict__ offsets,
-                      const int* __restrict__ tiles, const int* __restrict__ n_tiles, int n_feat, int K, int stages,
+                      const __grid_constant__ CUtensorMap map_x, void* __restrict__ out_, const int* offsets,
+                      const int* tiles, const int* n_tiles, int n_feat, int K, int stages,
                       int* status) {
     constexpr int FEATS = GATE ? TM_ROWS / 2 : TM_ROWS;        // output features per tile
     constexpr int X_BYTES = TM_TOK * BLOCK_K * 2;
@@ -136,9 +136,11 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const uint32_t tmem_base = tmem_base_slot;
     const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
     let_next_kernel_start();
-    // the list of row tiles, the rows themselves and their number come from the kernels before
+    // The list of row tiles, the rows themselves and their number come from the kernels before: they are
+    // read after the wait, through pointers that promise the compiler nothing (a `const __restrict__` load
+    // may be moved ahead of the wait, where the arrays still hold the previous layer's lists).
     wait_for_previous_kernels();
-    const int n_row_tiles = n_tiles[0];
+    const int n_row_tiles = *reinterpret_cast<const volatile int*>(n_tiles);
     const int total_tiles = n_row_tiles * n_feat_tiles;
     const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
@@ -267,7 +269,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     int stages = SMEM_BUDGET / STAGE_BYTES;
     if (stages > total_kb) stages = total_kb;
-    const size_t smem = (size_t)stages * STAGE_BYTES + 1024;
+    // Always the whole budget, also where fewer stages would do: a CTA then has its SM to itself, so no CTA
+    // of a kernel that starts early behind this one can sit on the same SM and wait for tensor memory
+    // (a CTA here takes all 512 columns).
+    const size_t smem = (size_t)SMEM_BUDGET + 1024;
     auto kernel = moe_grouped_tc_kernel<GATE>;
     static PerDeviceOnce configured;
     if (int rc = raise_dynamic_smem(kernel, SMEM_BUDGET + 1024, configured, "moe_grouped_tcgen05")) return rc;

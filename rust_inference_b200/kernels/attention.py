@@ -79,12 +79,15 @@ def decode_kernel(name: str):
 def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scale, window=0, chunk=0,
               v_head_dim=None, out_scale=1.0):
     """out[t] = softmax(q_t K^T * scale) V over the keys 0..pos(t) of t's slot.  q is the
-    leading n_heads*head_dim columns of `qkv`, already rotated.  `chunk`: only the keys of the
-    query's own block of that many positions; `v_head_dim`: values of another head size than
-    keys; `out_scale`: a factor on the result.  Those three are the generic kernel's."""
+    leading n_heads*head_dim columns of `qkv`, already rotated.  `window`: only the last so many
+    keys; `chunk`: only the keys of the query's own block of that many positions (counted from the
+    start of the sequence); `v_head_dim`: values of another head size than keys; `out_scale`: a
+    factor on the result.  The tensor-core kernels take a window or a chunk (as one signed span) and
+    equal head sizes; values of their own size, or both limits at once, are the generic kernel's."""
     q_ld = qkv.shape[1]
-    plain = not chunk and (v_head_dim is None or v_head_dim == head_dim) and out_scale == 1.0
-    if qkv.dtype == torch.bfloat16 and plain:
+    same_sizes = v_head_dim is None or v_head_dim == head_dim
+    if qkv.dtype == torch.bfloat16 and same_sizes and not (window and chunk):
+        span = window if window else -int(chunk or 0)
         decode = ctx.all_single
         if ops.attention_mma_supports(head_dim, ctx.page_size, n_heads, n_kv_heads, decode):
             if decode:
@@ -94,22 +97,28 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
                 if splits > 1 and name != "cluster":
                     part_o = ctx.buffer("attn_part_o", (ctx.n_seqs * n_heads * splits * head_dim,), torch.float32)
                     part_ml = ctx.buffer("attn_part_ml", (ctx.n_seqs * n_heads * splits * 2,), torch.float32)
-                return decode_kernel(name)(
+                decode_kernel(name)(
                     qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_len,
                     ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, n_heads=n_heads, n_kv_heads=n_kv_heads,
-                    head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, n_splits=splits,
+                    head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=span, n_splits=splits,
                     part_o=part_o, part_ml=part_ml)
+                if out_scale != 1.0:
+                    ops.scale_(out, out_scale)         # a step's few rows: not worth a parameter of three merges
+                return out
             from . import attention_tc
             if _PREFILL != "mma" and attention_tc.supports(head_dim, ctx.page_size, n_heads, n_kv_heads, q_ld,
                                                            out.shape[1]):
                 return attention_tc.prefill(
                     qkv, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens,
                     out, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, n_kv_heads=n_kv_heads,
-                    head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window)
-            return ops.attention_prefill(
+                    head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=span, out_scale=out_scale)
+            ops.attention_prefill(
                 qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.seq_slot, ctx.seq_start,
                 ctx.cu_seqlens, out, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads,
-                n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window)
+                n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=span)
+            if out_scale != 1.0:
+                ops.scale_(out, out_scale)
+            return out
     return ops.attention_generic(
         qkv, q_ld, cache_layer.k, cache_layer.v, ctx.page_table, ctx.token_pos, ctx.token_seq,
         ctx.seq_slot, out, n_tokens=qkv.shape[0], n_heads=n_heads, n_kv_heads=n_kv_heads,

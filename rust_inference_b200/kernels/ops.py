@@ -339,6 +339,14 @@ def cast(src: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (float32 arithmetic, one rounding); x float32 or bfloat16, contiguous, on the device."""
+    _need_cuda(x)
+    _need(x.is_contiguous(), "scale_: contiguous tensors only")
+    _call("elementwise", "ri_scale", _p(x), c_int(dtype_code(x.dtype)), c_longlong(x.numel()), c_float(factor), _stream())
+    return x
+
+
 def fill_normal(out: torch.Tensor, key: int, mean: float = 0.0, std: float = 1.0) -> torch.Tensor:
     """out[i] = mean + std * z_i with z_i a standard normal number that depends on (key, i) only
     (`sampling.rng.normal` restates it on the host).  out: float32 or bfloat16, contiguous, on the device."""
@@ -431,14 +439,34 @@ def attention_prefill(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, se
 # ----------------------------------------------------------------------------
 # A gated linear recurrence with a matrix state per head (csrc/recurrent.cu)
 # ----------------------------------------------------------------------------
+RECURRENCE_PIECE = 64           # tokens of a long run of new tokens that one block scans
+
+
+def recurrence_pieces(max_new: int, n_seqs: int, heads: int, dim: int, vdim: int, limit_bytes: int = 1 << 30) -> tuple:
+    """(piece, most pieces per sequence) for a step whose longest run of new tokens is max_new: (0, 1) for
+    short runs (one pass per sequence); else pieces of RECURRENCE_PIECE tokens, longer ones while the
+    scratch for their states would exceed limit_bytes."""
+    if max_new <= 2 * RECURRENCE_PIECE:
+        return 0, 1
+    piece = RECURRENCE_PIECE
+    while n_seqs * -(-max_new // piece) * heads * dim * (vdim + 1) * 4 > limit_bytes and piece < max_new:
+        piece *= 2
+    return piece, -(-max_new // piece)
+
+
 def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, norm_weight: torch.Tensor,
                      state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, *,
-                     n_seqs: int, heads: int, dim: int, vdim: int, eps: float, out_scale: float = 1.0) -> torch.Tensor:
+                     n_seqs: int, heads: int, dim: int, vdim: int, eps: float, out_scale: float = 1.0,
+                     o_raw: torch.Tensor | None = None, piece: int = 0, max_pieces: int = 1,
+                     scratch: torch.Tensor | None = None) -> torch.Tensor:
     """S <- diag(f) S + (1 - f) v^T, o = S^T q per head over every sequence's new tokens in order, then
     o / rms(o) * norm_weight * out_scale per head.  z: float32 [T, 2*heads*dim + heads*vdim] holding the
-    projections [q | f | v] before their activations (overwritten); state: float32 [slots, heads, dim,
-    vdim], read and left at the sequence's last token; out: [T, heads*vdim] in the run dtype."""
-    _need_cuda(z, bias, lower, norm_weight, state, cu_seqlens, seq_slot, out)
+    projections [q | f | v] before their activations (q and f are overwritten); state: float32 [slots, heads,
+    dim, vdim], read and left at the sequence's last token; out: [T, heads*vdim] in the run dtype; o_raw:
+    float32 [T, heads*vdim] scratch.  piece > 0: every sequence's new tokens are cut into pieces of that many
+    tokens (at most max_pieces per sequence) that are scanned side by side, their states in `scratch`
+    (float32, n_seqs * max_pieces * heads * dim * (vdim + 1) values): `recurrence_pieces` chooses."""
+    _need_cuda(z, bias, lower, norm_weight, state, cu_seqlens, seq_slot, out, o_raw, scratch)
     n = z.shape[0]
     _need(z.dtype == torch.float32 and z.is_contiguous() and z.shape[1] == 2 * heads * dim + heads * vdim,
           "gated_recurrence: z must be float32 [T, 2*heads*dim + heads*vdim]")
@@ -449,11 +477,22 @@ def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, n
     _need(out.is_contiguous() and out.shape == (n, heads * vdim), "gated_recurrence: out shape")
     _need(cu_seqlens.dtype == torch.int32 and seq_slot.dtype == torch.int32 and cu_seqlens.numel() >= n_seqs + 1
           and seq_slot.numel() >= n_seqs, "gated_recurrence: the step's arrays must be int32")
+    if o_raw is None:
+        o_raw = torch.empty((n, heads * vdim), dtype=torch.float32, device=z.device)
+    _need(o_raw.dtype == torch.float32 and o_raw.is_contiguous() and o_raw.numel() >= n * heads * vdim,
+          "gated_recurrence: o_raw must be float32 [T, heads*vdim]")
+    if piece > 0:
+        need = n_seqs * max_pieces * heads * dim * (vdim + 1)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=z.device)
+        _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= need,
+              "gated_recurrence: scratch too small for the pieces")
     _call("recurrent", "ri_gated_recurrence", _p(z), c_int(z.shape[1]), _p(bias), _p(lower), _p(norm_weight), _p(state),
-          _p(cu_seqlens), _p(seq_slot), _p(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(n_seqs), c_int(heads),
-          c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), _stream())
+          _p(cu_seqlens), _p(seq_slot), _p(o_raw), _p(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(n_seqs),
+          c_int(heads), c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), c_int(piece), c_int(max_pieces),
+          _p(scratch if piece > 0 else None), _stream())
     global _launches
-    _launches += 2                    # three kernels behind one entry point
+    _launches += 4 if piece > 0 else 2                    # several kernels behind one entry point
     return out
 
 

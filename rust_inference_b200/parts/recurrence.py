@@ -72,7 +72,15 @@ class GatedLinearRecurrence(Mixer):
         z = ctx.buffer("recurrence_z", (n, 2 * self.q_dim + self.v_dim), torch.float32)
         linear.logits(x, self.w_qfv, z, ctx)                       # float32 results in both precisions
         o = ctx.buffer("recurrence_o", (n, self.v_dim), self.dtype)
+        o_raw = ctx.buffer("recurrence_o_raw", (n, self.v_dim), torch.float32)
+        # long runs of new tokens are cut into pieces that are scanned side by side
+        piece, most = ops.recurrence_pieces(ctx.max_new, ctx.n_seqs, self.n_heads, self.head_dim, self.v_head_dim)
+        scratch = None
+        if piece:
+            scratch = ctx.buffer("recurrence_pieces", (ctx.n_seqs * most * self.n_heads * self.head_dim
+                                                       * (self.v_head_dim + 1),), torch.float32)
         ops.gated_recurrence(z, self.f_bias, self.lower, self.norm, cache_layer.state, ctx.cu_seqlens, ctx.seq_slot, o,
                              n_seqs=ctx.n_seqs, heads=self.n_heads, dim=self.head_dim, vdim=self.v_head_dim,
-                             eps=self.eps, out_scale=self.out_scale)
+                             eps=self.eps, out_scale=self.out_scale, o_raw=o_raw, piece=piece, max_pieces=most,
+                             scratch=scratch)
         linear.into_residual(o, self.w_o, residual, ctx)

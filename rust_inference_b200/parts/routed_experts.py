@@ -84,8 +84,9 @@ class RoutedExperts(FeedForward):
         return out
 
     # steps of more tokens than this run the experts' products on the tensor cores (tiles of 128 rows of one
-    # expert); smaller ones are bound by the chosen experts' weights, which the FFMA form streams in tiles of 32
-    TENSOR_CORE_MIN_TOKENS = 16
+    # expert, their weights streamed by TMA) when the sizes allow; the FFMA form is the 32-bit path and
+    # the fallback for other sizes
+    TENSOR_CORE_MIN_TOKENS = 0
 
     def _on_tensor_cores(self, x) -> bool:
         if x.dtype != torch.bfloat16 or x.shape[0] <= self.TENSOR_CORE_MIN_TOKENS:

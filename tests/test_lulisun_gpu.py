@@ -142,15 +142,16 @@ def test_grouped_expert_products_on_tensor_cores(experts, top, ff, width, n):
     assert rel_err(residual, want) < 2e-2
 
 
+@pytest.mark.parametrize("lens,cuts", [([23, 9], (100, 5, 2, 1, 100)), ([333, 150], (1000, 140, 64, 1000))])
 @pytest.mark.parametrize("heads,dim,vdim", [(2, 48, 32), (1, 72, 33), (3, 24, 40), (2, 8, 16), (1, 130, 70), (1, 300, 8)])
-def test_recurrence_in_portions_and_slots(heads, dim, vdim):
+def test_recurrence_in_portions_and_slots(heads, dim, vdim, lens, cuts):
     """The recurrence kernel over a whole sequence, and cut into portions of 1, 2 and 5 tokens with the
     state carried in the slot, for two sequences of unequal length in one call; then the slots are used
-    again from a zero state."""
+    again from a zero state.  Runs of more than 128 new tokens are cut into pieces that are scanned side by
+    side (the second set of lengths: whole, 140 + rest, 64 at a time)."""
     from rust_inference_b200.kernels import ops
     g = torch.Generator().manual_seed(dim)
     width, eps, scale = 64, 1e-5, 0.6
-    lens = [23, 9]
     w = {"q": torch.randn(heads * dim, width, generator=g) / 8, "f": torch.randn(heads * dim, width, generator=g) / 4,
          "f.b": torch.randn(heads * dim, generator=g), "lower": torch.rand(heads * dim, generator=g) * 0.95,
          "v": torch.randn(heads * vdim, width, generator=g) / 8, "norm": 1 + torch.randn(vdim, generator=g) * 0.2,
@@ -174,8 +175,11 @@ def test_recurrence_in_portions_and_slots(heads, dim, vdim):
             ends = [sum(take[b] for b in live[:i + 1]) for i in range(len(live))]
             cu = torch.tensor([0] + ends, dtype=torch.int32, device=DEV)
             out = torch.empty(z.shape[0], heads * vdim, dtype=torch.float32, device=DEV)
+            piece, most = ops.recurrence_pieces(max(take), len(live), heads, dim, vdim)
+            assert (piece > 0) == (max(take) > 128)
             ops.gated_recurrence(d(z), d(w["f.b"]), d(w["lower"]), d(w["norm"]), state, cu, slots[live].contiguous(), out,
-                                 n_seqs=len(live), heads=heads, dim=dim, vdim=vdim, eps=eps, out_scale=scale)
+                                 n_seqs=len(live), heads=heads, dim=dim, vdim=vdim, eps=eps, out_scale=scale,
+                                 piece=piece, max_pieces=most)
             o = 0
             for b in live:
                 outs[b].append(out[o:o + take[b]].cpu())
@@ -183,7 +187,7 @@ def test_recurrence_in_portions_and_slots(heads, dim, vdim):
                 at[b] += take[b]
         return [torch.cat(o) for o in outs]
 
-    for portions in (100, 5, 2, 1, 100):           # the last run uses the slots again
+    for portions in cuts:                           # the last run uses the slots again
         got = run(portions)
         for b in range(2):
             assert rel_err(got[b], want[b]) < 2e-5, (portions, b)
@@ -232,6 +236,53 @@ def test_chunk_edges_with_one_key_that_stands_out(dtype):
             if last + 1 < n:
                 assert not torch.allclose(out[last + 1, 0], 0.5 * vv[marked, 0].float(), atol=2e-2)
                 assert torch.allclose(out[last + 1, 0], 0.5 * vv[last + 1, 0].float(), atol=1e-2)   # alone in its chunk
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("chunk", [7, 64, 100, 200])
+def test_chunked_attention_on_tensor_cores(hd, chunk):
+    """The tensor-core kernels (tcgen05 prefill, split decode) with a chunk mask and an output factor against
+    the generic kernel on the same cache: continuations that start inside a chunk, query tiles that span
+    several chunks, decode steps just before, at and just after a chunk's first position."""
+    from types import SimpleNamespace
+    from rust_inference_b200.kernels import attention as attn_kernels, ops
+    heads, kvh, page = 4, 2, 64
+    g = torch.Generator().manual_seed(chunk + hd)
+    bf = torch.bfloat16
+    n_pages, max_pages = 24, 8                           # 512 positions per sequence
+    kc = d(torch.randn(n_pages, kvh, page, hd, generator=g).to(bf))
+    vc = d(torch.randn(n_pages, kvh, page, hd, generator=g).to(bf))
+    table = torch.stack([torch.randperm(n_pages, generator=g)[:max_pages] for _ in range(3)]).int()
+
+    def run(starts, news):
+        n = sum(news)
+        assert all(s + k <= max_pages * page for s, k in zip(starts, news))
+        pos = torch.cat([torch.arange(s, s + k) for s, k in zip(starts, news)]).int()
+        seq = torch.cat([torch.full((k,), b) for b, k in enumerate(news)]).int()
+        cu = torch.tensor([0] + [sum(news[:i + 1]) for i in range(len(news))], dtype=torch.int32)
+        ws = {}
+        ctx = SimpleNamespace(all_single=all(k == 1 for k in news), page_size=page, n_seqs=len(news), page_table=d(table),
+                              seq_slot=d(torch.arange(len(news), dtype=torch.int32)), seq_start=d(torch.tensor(starts, dtype=torch.int32)),
+                              seq_len=d(torch.tensor([s + k for s, k in zip(starts, news)], dtype=torch.int32)),
+                              cu_seqlens=d(cu), token_pos=d(pos), token_seq=d(seq), max_new=max(news), n_tokens=n,
+                              buffer=lambda name, shape, dtype: ws.setdefault((name, tuple(shape)), torch.empty(shape, dtype=dtype, device=DEV)))
+        qkv = d((torch.randn(n, (heads + 2 * kvh) * hd, generator=g) * 0.5).to(bf))
+        fast = torch.empty(n, heads * hd, dtype=bf, device=DEV)
+        attn_kernels.attention(qkv, SimpleNamespace(k=kc, v=vc), fast, ctx, n_heads=heads, n_kv_heads=kvh, head_dim=hd,
+                               scale=0.11, chunk=chunk, out_scale=0.7)
+        plain = torch.empty(n, heads * hd, dtype=bf, device=DEV)
+        ops.attention_generic(qkv, qkv.shape[1], kc, vc, ctx.page_table, ctx.token_pos, ctx.token_seq, ctx.seq_slot, plain,
+                              n_tokens=n, n_heads=heads, n_kv_heads=kvh, head_dim=hd, page_size=page, scale=0.11, chunk=chunk,
+                              out_scale=0.7)
+        torch.cuda.synchronize()
+        from rust_inference_b200.kernels import tcgen05
+        tcgen05.check_status()
+        assert rel_err(fast, plain) < 2e-2, (starts, news)
+
+    run([0, 70, 5], [300, 150, 1])                       # prompts and continuations, a single token among them
+    run([chunk - 1, chunk, min(3 * chunk - 1, 440)], [130, 2, 64])        # every sequence stays within its 8 pages
+    for base in (chunk - 1, chunk, chunk + 1, 2 * chunk, 200, 449):
+        run([base, base + 1, max(0, base - 1)], [1, 1, 1])     # decode steps around a chunk's first position
 
 
 def test_partial_rotation_and_value_cache():
