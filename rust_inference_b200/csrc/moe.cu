@@ -45,8 +45,8 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-constexpr int ROUTE_WARPS = 8;
-constexpr int ROUTE_TOKENS = 4;           // most tokens a block routes: the router's rows are read once for all of them
+constexpr int ROUTE_WARPS = 16;
+constexpr int ROUTE_TOKENS = 8;           // most tokens a block routes: the router's rows are read once for all of them
 
 template <typename T> __device__ __forceinline__ void load4_f32(const T* p, float* o);
 template <> __device__ __forceinline__ void load4_f32<float>(const float* p, float* o) {
@@ -84,6 +84,7 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
 #pragma unroll
         for (int k = 0; k < ROUTE_TOKENS; ++k) acc[k] = 0.f;
         if (VEC) {
+#pragma unroll 4
             for (int d = lane * 4; d < width; d += 128) {
                 const float4 w4 = *reinterpret_cast<const float4*>(w + d);
 #pragma unroll
@@ -345,7 +346,7 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
     if ((long long)keep * (experts / groups) < top)
         return fail("moe_route: %d groups of %d experts cannot give %d choices", keep, experts / groups, top);
     // few tokens: one per block, so that the router's rows are shared out over more SMs
-    const int per_block = n_tokens >= 4 * 148 * ROUTE_TOKENS ? ROUTE_TOKENS : (n_tokens >= 2 * 148 ? 2 : 1);
+    const int per_block = n_tokens >= 148 * ROUTE_TOKENS ? ROUTE_TOKENS : (n_tokens >= 2 * 148 ? 2 : 1);
     const size_t smem = (size_t)per_block * (2 * experts + groups) * sizeof(float);
     if (smem > 48 * 1024) return fail("moe_route: %d experts exceed the router kernel's shared memory", experts);
     const int blocks = (n_tokens + per_block - 1) / per_block;

@@ -47,8 +47,9 @@ __global__ void recurrence_prepare_kernel(float* __restrict__ z, int ld, const f
 
 // Threads of a warp: lane = column_in_warp * R + r.  Thread (r, j) keeps ROWS consecutive rows
 // (r * ROWS ...) of column j of the state in registers; the sum over rows of S[i, j] q[i] is finished by
-// log2(R) shuffles inside the warp.  No block-wide barrier in the loop, and the next token's q, f and v
-// are on their way while the current one is worked on.
+// log2(R) shuffles inside the warp.  The tokens' q, f and v come through shared memory in tiles of up to 64
+// tokens, fetched by all threads at once with cp.async (a token's gates are shared by the block's columns),
+// so the loop over a tile's tokens touches no global memory but its one store of o.
 //
 // A long run of new tokens is cut into pieces of `piece` tokens that run side by side (three passes):
 //   LOCAL   every piece from a zero state: its end state and the product of its gates go to scratch
@@ -62,46 +63,34 @@ constexpr int COLS = 32;             // value columns per block
 constexpr int SCAN_THREADS = R * COLS;
 enum ScanMode { WHOLE = 0, LOCAL = 1, FINAL = 2 };
 
+// Shared memory of the scan: tiles of up to `tile_t` tokens, per token f and q as [R][ROWS + 4] (a slice of
+// ROWS channels per row slice, padded so that the eight slices' 16-byte reads fall into different banks;
+// channels beyond `dim` stay zero) and the block's COLS values of v.
 template <int ROWS>
-struct TokenRegs {
-    float f[ROWS], q[ROWS], v;
+struct ScanTile {
+    static constexpr int SLICE = ROWS + 4;
+    static constexpr int TOKEN = 2 * R * SLICE + COLS;          // floats per token
 };
 
-template <int ROWS, bool VEC>
-__device__ __forceinline__ void load_token(TokenRegs<ROWS>& reg, const float* row, int q_off, int f_off, int v_off,
-                                           int i0, int dim, bool live) {
-    if (VEC) {
-#pragma unroll
-        for (int k = 0; k < ROWS; k += 4) {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-            if (i0 + k < dim) {                                   // dim is a multiple of 4 here
-                a = *reinterpret_cast<const float4*>(row + f_off + i0 + k);
-                b = *reinterpret_cast<const float4*>(row + q_off + i0 + k);
-            }
-            reg.f[k] = a.x; reg.f[k + 1] = a.y; reg.f[k + 2] = a.z; reg.f[k + 3] = a.w;
-            reg.q[k] = b.x; reg.q[k + 1] = b.y; reg.q[k + 2] = b.z; reg.q[k + 3] = b.w;
-        }
-    } else {
-#pragma unroll
-        for (int k = 0; k < ROWS; ++k) {
-            const bool in = i0 + k < dim;
-            reg.f[k] = in ? row[f_off + i0 + k] : 0.f;
-            reg.q[k] = in ? row[q_off + i0 + k] : 0.f;
-        }
-    }
-    reg.v = live ? row[v_off] : 0.f;
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <int ROWS, bool VEC>
-__global__ void __launch_bounds__(SCAN_THREADS, ROWS <= 16 ? 2 : 1)
+template <int ROWS, bool VEC, int mode>
+__global__ void __launch_bounds__(SCAN_THREADS)
 recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float* state,
                        float* piece_state, float* piece_gates, const int* __restrict__ cu_seqlens,
-                       const int* __restrict__ seq_slot, int heads, int dim, int vdim, int mode, int piece, int max_pieces) {
+                       const int* __restrict__ seq_slot, int heads, int dim, int vdim, int piece, int max_pieces,
+                       int tile_t) {
+    using Tile = ScanTile<ROWS>;
+    extern __shared__ __align__(16) float tile[];
     const int b = blockIdx.x / max_pieces, c = blockIdx.x % max_pieces, h = blockIdx.y;
-    const int r = threadIdx.x % R;
-    const int j = blockIdx.z * COLS + threadIdx.x / R;
+    const int r = threadIdx.x % R, jj = threadIdx.x / R;
+    const int j0 = blockIdx.z * COLS, j = j0 + jj;
     const bool live = j < vdim;
     const int i0 = r * ROWS;
+    for (int i = threadIdx.x; i < tile_t * Tile::TOKEN; i += SCAN_THREADS) tile[i] = 0.f;
     let_next_kernel_start();
     wait_for_previous_kernels();
     const int t0 = cu_seqlens[b] + c * piece;
@@ -123,34 +112,81 @@ recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float*
         g[k] = 1.f;
     }
     const int qdim = heads * dim;
-    const int q_off = h * dim, f_off = qdim + h * dim, v_off = 2 * qdim + h * vdim + j;
+    const int q_off = h * dim, f_off = qdim + h * dim, v_off = 2 * qdim + h * vdim + j0;
+    const int cols = min(COLS, vdim - j0);
     const int o_ld = heads * vdim;
-    TokenRegs<ROWS> cur, nxt;
-    load_token<ROWS, VEC>(nxt, z + (size_t)t0 * ld, q_off, f_off, v_off, i0, dim, live);
-    for (int t = t0; t < t1; ++t) {
-        cur = nxt;
-        if (t + 1 < t1) load_token<ROWS, VEC>(nxt, z + (size_t)(t + 1) * ld, q_off, f_off, v_off, i0, dim, live);
-        float acc0 = 0.f, acc1 = 0.f;
-#pragma unroll
-        for (int k = 0; k < ROWS; ++k) {
-            const float fi = cur.f[k];
-            s[k] = fmaf(fi, s[k], fmaf(-fi, cur.v, cur.v));          // f s + (1 - f) v; rows beyond dim: f = 0, q = 0
-            if (mode == LOCAL) g[k] *= fi;
-            if (k & 1) acc1 = fmaf(s[k], cur.q[k], acc1); else acc0 = fmaf(s[k], cur.q[k], acc0);
+    __syncthreads();                                              // the zeros are in place
+
+    for (int tb = t0; tb < t1; tb += tile_t) {
+        const int n_tok = min(tile_t, t1 - tb);
+        // ---- the tile's q, f and v into shared memory, all threads, everything in flight at once ----
+        if (VEC) {
+            const int per = dim / 2 + cols / 4;                   // 16-byte items per token: f, q, v
+            for (int idx = threadIdx.x; idx < n_tok * per; idx += SCAN_THREADS) {
+                const int tok = idx / per, it = idx % per;
+                const float* row = z + (size_t)(tb + tok) * ld;
+                float* base = tile + tok * Tile::TOKEN;
+                if (it < dim / 4) {
+                    const int ch = 4 * it;
+                    cp_async16(base + (ch / ROWS) * Tile::SLICE + ch % ROWS, row + f_off + ch);
+                } else if (it < dim / 2) {
+                    const int ch = 4 * (it - dim / 4);
+                    if (mode != LOCAL)                            // a piece's end state needs no q
+                        cp_async16(base + R * Tile::SLICE + (ch / ROWS) * Tile::SLICE + ch % ROWS, row + q_off + ch);
+                } else {
+                    const int cc = 4 * (it - dim / 2);
+                    cp_async16(base + 2 * R * Tile::SLICE + cc, row + v_off + cc);
+                }
+            }
+            cp_async_wait_all();
+        } else {
+            const int per = 2 * dim + cols;
+            for (int idx = threadIdx.x; idx < n_tok * per; idx += SCAN_THREADS) {
+                const int tok = idx / per, it = idx % per;
+                const float* row = z + (size_t)(tb + tok) * ld;
+                float* base = tile + tok * Tile::TOKEN;
+                if (it < dim) base[(it / ROWS) * Tile::SLICE + it % ROWS] = row[f_off + it];
+                else if (it < 2 * dim) base[R * Tile::SLICE + ((it - dim) / ROWS) * Tile::SLICE + (it - dim) % ROWS] = row[q_off + it - dim];
+                else base[2 * R * Tile::SLICE + it - 2 * dim] = row[v_off + it - 2 * dim];
+            }
         }
-        if (mode != LOCAL) {
-            float acc = acc0 + acc1;
+        __syncthreads();
+        // ---- the recurrence over the tile, out of shared memory ----
+        for (int tok = 0; tok < n_tok; ++tok) {
+            const float* base = tile + tok * Tile::TOKEN;
+            const float4* f4 = reinterpret_cast<const float4*>(base + r * Tile::SLICE);
+            const float4* q4 = reinterpret_cast<const float4*>(base + R * Tile::SLICE + r * Tile::SLICE);
+            const float v = base[2 * R * Tile::SLICE + jj];       // columns beyond vdim: zero, never stored
+            float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-            for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (live && r == 0) o_raw[(size_t)t * o_ld + h * vdim + j] = acc;
+            for (int k4 = 0; k4 < ROWS / 4; ++k4) {
+                const float4 fv = f4[k4], qv = mode != LOCAL ? q4[k4] : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float ff[4] = {fv.x, fv.y, fv.z, fv.w}, qq[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int k = 4 * k4 + u;
+                    s[k] = fmaf(ff[u], s[k], fmaf(-ff[u], v, v));      // f s + (1 - f) v; channels beyond dim: f = 0, q = 0
+                    if (mode == LOCAL) g[k] *= ff[u];
+                    if (mode != LOCAL) {
+                        if (u & 1) acc1 = fmaf(s[k], qq[u], acc1); else acc0 = fmaf(s[k], qq[u], acc0);
+                    }
+                }
+            }
+            if (mode != LOCAL) {
+                float acc = acc0 + acc1;
+#pragma unroll
+                for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (live && r == 0) o_raw[(size_t)(tb + tok) * o_ld + h * vdim + j] = acc;
+            }
         }
+        __syncthreads();                                          // the tile may be overwritten
     }
     if (mode != FINAL) {
 #pragma unroll
         for (int k = 0; k < ROWS; ++k)
             if (live && i0 + k < dim) S[(size_t)(i0 + k) * vdim + j] = s[k];
     }
-    if (mode == LOCAL && blockIdx.z == 0 && threadIdx.x / R == 0) {
+    if (mode == LOCAL && blockIdx.z == 0 && jj == 0) {
         float* G = piece_gates + ((size_t)blockIdx.x * heads + h) * dim;
 #pragma unroll
         for (int k = 0; k < ROWS; ++k)
@@ -204,15 +240,34 @@ __global__ void headwise_rmsnorm_kernel(const float* x, int ld, int col0, const 
 }
 
 
+constexpr int SCAN_SMEM_LIMIT = 96 * 1024;       // two blocks to an SM
+
 template <int ROWS>
-cudaError_t launch_scan(bool vec, dim3 grid, cudaStream_t stream, const float* z, int ld, float* o_raw, float* state,
-                        float* piece_state, float* piece_gates, const int* cu_seqlens, const int* seq_slot, int heads, int dim,
-                        int vdim, int mode, int piece, int max_pieces) {
-    if (vec && ROWS % 4 == 0)
-        return launch_dependent(recurrence_scan_kernel<ROWS, (ROWS % 4 == 0)>, grid, SCAN_THREADS, 0, stream, z, ld, o_raw, state,
-                                piece_state, piece_gates, cu_seqlens, seq_slot, heads, dim, vdim, mode, piece, max_pieces);
-    return launch_dependent(recurrence_scan_kernel<ROWS, false>, grid, SCAN_THREADS, 0, stream, z, ld, o_raw, state,
-                            piece_state, piece_gates, cu_seqlens, seq_slot, heads, dim, vdim, mode, piece, max_pieces);
+int launch_scan(bool vec, dim3 grid, cudaStream_t stream, const float* z, int ld, float* o_raw, float* state,
+                float* piece_state, float* piece_gates, const int* cu_seqlens, const int* seq_slot, int heads, int dim,
+                int vdim, int mode, int piece, int max_pieces, int longest) {
+    const int token_bytes = ScanTile<ROWS>::TOKEN * (int)sizeof(float);
+    int tile_t = SCAN_SMEM_LIMIT / token_bytes;
+    if (tile_t > 64) tile_t = 64;
+    if (tile_t > longest) tile_t = longest;                      // a decode step brings one token
+    if (tile_t < 1) return fail("gated_recurrence: a token's %d bytes of gates do not fit shared memory", token_bytes);
+    const size_t smem = (size_t)tile_t * token_bytes;
+    cudaError_t e = cudaSuccess;
+#define RI_LAUNCH(V, M)                                                                                                   \
+    {                                                                                                                     \
+        auto kernel = recurrence_scan_kernel<ROWS, V, M>;                                                                 \
+        static PerDeviceOnce once;                                                                                        \
+        if (int rc = raise_dynamic_smem(kernel, SCAN_SMEM_LIMIT, once, "gated_recurrence")) return rc;                    \
+        e = launch_dependent(kernel, grid, SCAN_THREADS, smem, stream, z, ld, o_raw, state, piece_state, piece_gates,     \
+                             cu_seqlens, seq_slot, heads, dim, vdim, piece, max_pieces, tile_t);                          \
+    }
+    if (vec) {
+        if (mode == WHOLE) RI_LAUNCH(true, WHOLE) else if (mode == LOCAL) RI_LAUNCH(true, LOCAL) else RI_LAUNCH(true, FINAL)
+    } else {
+        if (mode == WHOLE) RI_LAUNCH(false, WHOLE) else if (mode == LOCAL) RI_LAUNCH(false, LOCAL) else RI_LAUNCH(false, FINAL)
+    }
+#undef RI_LAUNCH
+    return check_launch(e, "gated_recurrence (scan)");
 }
 
 }  // namespace
@@ -227,10 +282,11 @@ RI_API long long ri_gated_recurrence_scratch(int n_seqs, int max_pieces, int hea
 // out: [n_tokens, heads*vdim] in `dtype`.  piece > 0: sequences' new tokens are cut into pieces of that many
 // tokens, at most max_pieces per sequence (the longest run of new tokens / piece, rounded up), worked on side
 // by side with `scratch` (ri_gated_recurrence_scratch floats); piece == 0: one pass per sequence.
+// longest_run: the most new tokens any sequence brings (0: unknown), which sizes the scan's shared memory.
 RI_API int ri_gated_recurrence(float* z, int ld, const float* bias, const float* low, const float* norm_w,
                                float* state, const int* cu_seqlens, const int* seq_slot, float* o_raw, void* out, int dtype,
                                int n_tokens, int n_seqs, int heads, int dim, int vdim, float eps, float out_scale,
-                               int piece, int max_pieces, float* scratch, cudaStream_t stream) {
+                               int piece, int max_pieces, float* scratch, int longest_run, cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (ld < 2 * heads * dim + heads * vdim) return fail("gated_recurrence: rows of %d values are too short", ld);
     if (heads > 65535) return fail("gated_recurrence: %d heads exceed the grid limit", heads);
@@ -245,23 +301,22 @@ RI_API int ri_gated_recurrence(float* z, int ld, const float* bias, const float*
         cudaError_t e = launch_dependent(recurrence_prepare_kernel, blocks, 256, 0, stream, z, ld, bias, low, n_tokens, qdim);
         if (check_launch(e, "gated_recurrence (prepare)")) return 1;
     }
-    const bool vec = dim % 4 == 0 && ld % 4 == 0 && (uintptr_t)z % 16 == 0;
+    const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && (uintptr_t)z % 16 == 0;
     const int col_tiles = (vdim + COLS - 1) / COLS;
     float* piece_state = scratch;
     float* piece_gates = piece > 0 ? scratch + (size_t)n_seqs * max_pieces * heads * dim * vdim : nullptr;
     auto scan = [&](int mode) -> int {
         const int mp = mode == WHOLE ? 1 : max_pieces;
         dim3 grid(n_seqs * mp, heads, col_tiles);
-        cudaError_t e;
+        const int longest = mode == WHOLE ? (longest_run > 0 ? longest_run : n_tokens) : piece;
 #define RI_SCAN(ROWS) launch_scan<ROWS>(vec, grid, stream, z, ld, o_raw, state, piece_state, piece_gates, cu_seqlens, seq_slot, \
-                                        heads, dim, vdim, mode, piece > 0 ? piece : 1, mp)
-        if (rows == 4) e = RI_SCAN(4);
-        else if (rows == 8) e = RI_SCAN(8);
-        else if (rows == 16) e = RI_SCAN(16);
-        else if (rows == 32) e = RI_SCAN(32);
-        else e = RI_SCAN(64);
+                                        heads, dim, vdim, mode, piece > 0 ? piece : 1, mp, longest)
+        if (rows == 4) return RI_SCAN(4);
+        if (rows == 8) return RI_SCAN(8);
+        if (rows == 16) return RI_SCAN(16);
+        if (rows == 32) return RI_SCAN(32);
+        return RI_SCAN(64);
 #undef RI_SCAN
-        return check_launch(e, "gated_recurrence (scan)");
     };
     if (piece <= 0) {
         if (scan(WHOLE)) return 1;

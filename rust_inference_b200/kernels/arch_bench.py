@@ -69,8 +69,16 @@ class Timer:
         return times[len(times) // 2]
 
 
-def _roofline_ms(flops: float, bytes_: float, peaks: dict) -> float:
-    return max(flops / (peaks["bf16_tflops"] * 1e12), bytes_ / (peaks["hbm_gbs"] * 1e9)) * 1e3
+def _roofline_ms(flops: float, bytes_: float, peaks: dict, fp32_flops: float = 0.0) -> float:
+    return max(flops / (peaks["bf16_tflops"] * 1e12), bytes_ / (peaks["hbm_gbs"] * 1e9),
+               fp32_flops / (peaks["fp32_ffma_tflops_nominal"] * 1e12)) * 1e3
+
+
+def ffma_peak_tflops() -> float:
+    """Nominal float32 throughput of the FFMA pipe: SMs x 128 lanes x 2 x the SM clock (not measured)."""
+    p = torch.cuda.get_device_properties(torch.cuda.current_device())
+    khz = getattr(p, "clock_rate", 0) or 1_965_000
+    return p.multi_processor_count * 128 * 2 * khz * 1e3 / 1e12
 
 
 def _step_context(engine, lens_before: list, new_tokens: int, vocab: int, seed: int):
@@ -116,10 +124,12 @@ def time_parts(engine, kind: str, s: dict, lens_before: list, new_tokens: int, p
         kv_bytes += (last + 1 - first) * kv * 2 * hd * 2
     qo_bytes = n * heads * hd * 2 * 2
 
-    def row(name, ms, flops, bytes_):
-        ideal = _roofline_ms(flops, bytes_, peaks)
+    def row(name, ms, flops, bytes_, fp32_flops=0.0):
+        ideal = _roofline_ms(flops, bytes_, peaks, fp32_flops)
+        times = {"tensor": flops / (peaks["bf16_tflops"] * 1e12), "hbm": bytes_ / (peaks["hbm_gbs"] * 1e9),
+                 "ffma": fp32_flops / (peaks["fp32_ffma_tflops_nominal"] * 1e12)}
         out[name] = {"ms": round(ms, 4), "roofline_ms": round(ideal, 4), "x_roofline": round(ms / ideal, 2),
-                     "bound": "tensor" if flops / (peaks["bf16_tflops"] * 1e12) > bytes_ / (peaks["hbm_gbs"] * 1e9) else "hbm"}
+                     "bound": max(times, key=times.get)}
 
     if kind == "lulisun":
         left, right = (m for _, m in block.mixer.members)
@@ -143,11 +153,12 @@ def time_parts(engine, kind: str, s: dict, lens_before: list, new_tokens: int, p
         def recur():
             ops.gated_recurrence(z, right.f_bias, right.lower, right.norm, state_layer.state, ctx.cu_seqlens, ctx.seq_slot, o,
                                  n_seqs=ctx.n_seqs, heads=rh, dim=hd, vdim=hd, eps=1e-5, out_scale=0.7, o_raw=o_raw,
-                                 piece=piece, max_pieces=most, scratch=scratch)
+                                 piece=piece, max_pieces=most, scratch=scratch, longest_run=ctx.max_new)
         ms = timer(recur)
         # z read and (its q, f and v columns) written once, o written, the state of every sequence read and written
         rec_bytes = n * zw * 4 * 2 + n * rh * hd * 2 + 2 * len(lens_before) * rh * hd * hd * 4
-        row("recurrence", ms, 0.0, rec_bytes)
+        # and, per token, head and state element, three float32 multiply-adds that no tensor core may take
+        row("recurrence", ms, 0.0, rec_bytes, fp32_flops=6.0 * n * rh * hd * hd)
         ff = block.feed_forward
         out["feed_forward_ms"] = round(timer(lambda: ff.forward(x, residual, ctx)), 4)
         # the routed products alone: routing as the model does it on these activations
@@ -246,6 +257,7 @@ def main(sizes: str, peaks: dict, peak_source: str, *, prefill_tokens: int = 204
         context = s["chunk"] + s["chunk"] // 4        # a quarter into a chunk: the decode step sees that many keys
     torch.cuda.set_device(0)
     timer = Timer("cuda:0")
+    peaks = dict(peaks, fp32_ffma_tflops_nominal=round(ffma_peak_tflops(), 1))
     cache_tokens = batch * (context + steps + 128) + prefill_tokens + 4096
     result = {"arch": "lulisun", "sizes": sizes, "config": s, "dtype": "bf16", "data": "synthetic (random weights, random token ids)",
               "peaks": dict(peaks, source=peak_source), "l2": "256 MiB written between timed iterations"}

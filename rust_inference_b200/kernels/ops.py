@@ -458,14 +458,15 @@ def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, n
                      state: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, out: torch.Tensor, *,
                      n_seqs: int, heads: int, dim: int, vdim: int, eps: float, out_scale: float = 1.0,
                      o_raw: torch.Tensor | None = None, piece: int = 0, max_pieces: int = 1,
-                     scratch: torch.Tensor | None = None) -> torch.Tensor:
+                     scratch: torch.Tensor | None = None, longest_run: int = 0) -> torch.Tensor:
     """S <- diag(f) S + (1 - f) v^T, o = S^T q per head over every sequence's new tokens in order, then
     o / rms(o) * norm_weight * out_scale per head.  z: float32 [T, 2*heads*dim + heads*vdim] holding the
     projections [q | f | v] before their activations (q and f are overwritten); state: float32 [slots, heads,
     dim, vdim], read and left at the sequence's last token; out: [T, heads*vdim] in the run dtype; o_raw:
     float32 [T, heads*vdim] scratch.  piece > 0: every sequence's new tokens are cut into pieces of that many
     tokens (at most max_pieces per sequence) that are scanned side by side, their states in `scratch`
-    (float32, n_seqs * max_pieces * heads * dim * (vdim + 1) values): `recurrence_pieces` chooses."""
+    (float32, n_seqs * max_pieces * heads * dim * (vdim + 1) values): `recurrence_pieces` chooses.
+    longest_run: the most new tokens any sequence brings (0: unknown), which sizes the scan's shared memory."""
     _need_cuda(z, bias, lower, norm_weight, state, cu_seqlens, seq_slot, out, o_raw, scratch)
     n = z.shape[0]
     _need(z.dtype == torch.float32 and z.is_contiguous() and z.shape[1] == 2 * heads * dim + heads * vdim,
@@ -490,7 +491,7 @@ def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, n
     _call("recurrent", "ri_gated_recurrence", _p(z), c_int(z.shape[1]), _p(bias), _p(lower), _p(norm_weight), _p(state),
           _p(cu_seqlens), _p(seq_slot), _p(o_raw), _p(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(n_seqs),
           c_int(heads), c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), c_int(piece), c_int(max_pieces),
-          _p(scratch if piece > 0 else None), _stream())
+          _p(scratch if piece > 0 else None), c_int(max(0, min(int(longest_run), n))), _stream())
     global _launches
     _launches += 4 if piece > 0 else 2                    # several kernels behind one entry point
     return out

@@ -82,5 +82,5 @@ class GatedLinearRecurrence(Mixer):
         ops.gated_recurrence(z, self.f_bias, self.lower, self.norm, cache_layer.state, ctx.cu_seqlens, ctx.seq_slot, o,
                              n_seqs=ctx.n_seqs, heads=self.n_heads, dim=self.head_dim, vdim=self.v_head_dim,
                              eps=self.eps, out_scale=self.out_scale, o_raw=o_raw, piece=piece, max_pieces=most,
-                             scratch=scratch)
+                             scratch=scratch, longest_run=ctx.max_new)
         linear.into_residual(o, self.w_o, residual, ctx)

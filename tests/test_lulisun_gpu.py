@@ -179,7 +179,7 @@ def test_recurrence_in_portions_and_slots(heads, dim, vdim, lens, cuts):
             assert (piece > 0) == (max(take) > 128)
             ops.gated_recurrence(d(z), d(w["f.b"]), d(w["lower"]), d(w["norm"]), state, cu, slots[live].contiguous(), out,
                                  n_seqs=len(live), heads=heads, dim=dim, vdim=vdim, eps=eps, out_scale=scale,
-                                 piece=piece, max_pieces=most)
+                                 piece=piece, max_pieces=most, longest_run=max(take))
             o = 0
             for b in live:
                 outs[b].append(out[o:o + take[b]].cpu())
