@@ -139,11 +139,15 @@ class LulisunConfig:
                     raise ConfigError(f"config.json: {mw}.router: {m.experts} experts in {m.groups} groups, {m.keep} kept, "
                                       f"cannot give {m.top} choices")
             of = entry.get("weights_of")
-            if of is not None:
-                if isinstance(of, bool) or not isinstance(of, int) or not 0 <= of < len(entries) or of == i:
-                    raise ConfigError(f"config.json: {where}.weights_of {of!r} names no other layer")
-                if entries[of].get("weights_of") is not None:
-                    raise ConfigError(f"config.json: {where}.weights_of names layer {of}, which has no tensors of its own")
+            seen = {i}
+            while of is not None:                 # a layer may name one that itself runs another's tensors: follow to the owner
+                if isinstance(of, bool) or not isinstance(of, int) or not 0 <= of < len(entries) or of in seen:
+                    raise ConfigError(f"config.json: {where}.weights_of {entry.get('weights_of')!r} names no other layer "
+                                      "with tensors of its own")
+                if entries[of].get("weights_of") is None:
+                    break
+                seen.add(of)
+                of = entries[of].get("weights_of")
             layers.append(LulisunLayerConfig(a, r, _float(mixer, "left_scale", where + ".mixer"),
                                              _float(mixer, "right_scale", where + ".mixer"), m, of, raw=entry))
         eps = _float(_get(d, "norm", "the model"), "eps", "norm")

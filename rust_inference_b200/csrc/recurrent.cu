@@ -46,7 +46,8 @@ __global__ void recurrence_prepare_kernel(float* __restrict__ z, int ld, const f
 }
 
 // Threads of a warp: lane = column_in_warp * R + r.  Thread (r, j) keeps ROWS consecutive rows
-// (r * ROWS ...) of column j of the state in registers; the sum over rows of S[i, j] q[i] is finished by
+// (r * ROWS ...) of columns j and j + 32 of the state in registers (its gates and query values, read once
+// per token from shared memory, serve both columns: the scan is bound by those reads); the sum over rows of S[i, j] q[i] is finished by
 // log2(R) shuffles inside the warp.  The tokens' q, f and v come through shared memory in tiles of up to 64
 // tokens, fetched by all threads at once with cp.async (a token's gates are shared by the block's columns),
 // so the loop over a tile's tokens touches no global memory but its one store of o.
@@ -59,8 +60,9 @@ __global__ void recurrence_prepare_kernel(float* __restrict__ z, int ld, const f
 // A short run (one piece per sequence: decode steps, small portions) is one pass, WHOLE: from the
 // slot's state, writing o and the slot's state.
 constexpr int R = 8;                 // row slices per column
-constexpr int COLS = 32;             // value columns per block
-constexpr int SCAN_THREADS = R * COLS;
+constexpr int CPT = 2;               // value columns per thread: a thread's gates serve both
+constexpr int COLS = 32 * CPT;       // value columns per block
+constexpr int SCAN_THREADS = R * 32;
 enum ScanMode { WHOLE = 0, LOCAL = 1, FINAL = 2 };
 
 // Shared memory of the scan: tiles of up to `tile_t` tokens, per token f and q as [R][ROWS + 4] (a slice of
@@ -87,8 +89,7 @@ recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float*
     extern __shared__ __align__(16) float tile[];
     const int b = blockIdx.x / max_pieces, c = blockIdx.x % max_pieces, h = blockIdx.y;
     const int r = threadIdx.x % R, jj = threadIdx.x / R;
-    const int j0 = blockIdx.z * COLS, j = j0 + jj;
-    const bool live = j < vdim;
+    const int j0 = blockIdx.z * COLS;                            // the thread's columns: j0 + jj + 32 c
     const int i0 = r * ROWS;
     for (int i = threadIdx.x; i < tile_t * Tile::TOKEN; i += SCAN_THREADS) tile[i] = 0.f;
     let_next_kernel_start();
@@ -105,12 +106,18 @@ recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float*
     } else {
         S = piece_state + (((size_t)blockIdx.x * heads + h) * dim) * vdim;
     }
-    float s[ROWS], g[ROWS];
+    bool live[CPT];
+    float s[CPT][ROWS], g[ROWS];
 #pragma unroll
-    for (int k = 0; k < ROWS; ++k) {
-        s[k] = (mode != LOCAL && live && i0 + k < dim) ? S[(size_t)(i0 + k) * vdim + j] : 0.f;
-        g[k] = 1.f;
+    for (int cc = 0; cc < CPT; ++cc) {
+        const int j = j0 + jj + 32 * cc;
+        live[cc] = j < vdim;
+#pragma unroll
+        for (int k = 0; k < ROWS; ++k)
+            s[cc][k] = (mode != LOCAL && live[cc] && i0 + k < dim) ? S[(size_t)(i0 + k) * vdim + j] : 0.f;
     }
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) g[k] = 1.f;
     const int qdim = heads * dim;
     const int q_off = h * dim, f_off = qdim + h * dim, v_off = 2 * qdim + h * vdim + j0;
     const int cols = min(COLS, vdim - j0);
@@ -156,8 +163,12 @@ recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float*
             const float* base = tile + tok * Tile::TOKEN;
             const float4* f4 = reinterpret_cast<const float4*>(base + r * Tile::SLICE);
             const float4* q4 = reinterpret_cast<const float4*>(base + R * Tile::SLICE + r * Tile::SLICE);
-            const float v = base[2 * R * Tile::SLICE + jj];       // columns beyond vdim: zero, never stored
-            float acc0 = 0.f, acc1 = 0.f;
+            float v[CPT], acc0[CPT], acc1[CPT];
+#pragma unroll
+            for (int cc = 0; cc < CPT; ++cc) {
+                v[cc] = base[2 * R * Tile::SLICE + jj + 32 * cc];    // columns beyond vdim: zero, never stored
+                acc0[cc] = acc1[cc] = 0.f;
+            }
 #pragma unroll
             for (int k4 = 0; k4 < ROWS / 4; ++k4) {
                 const float4 fv = f4[k4], qv = mode != LOCAL ? q4[k4] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -165,26 +176,35 @@ recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float*
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int k = 4 * k4 + u;
-                    s[k] = fmaf(ff[u], s[k], fmaf(-ff[u], v, v));      // f s + (1 - f) v; channels beyond dim: f = 0, q = 0
                     if (mode == LOCAL) g[k] *= ff[u];
-                    if (mode != LOCAL) {
-                        if (u & 1) acc1 = fmaf(s[k], qq[u], acc1); else acc0 = fmaf(s[k], qq[u], acc0);
+#pragma unroll
+                    for (int cc = 0; cc < CPT; ++cc) {
+                        // f s + (1 - f) v; channels beyond dim: f = 0, q = 0
+                        s[cc][k] = fmaf(ff[u], s[cc][k], fmaf(-ff[u], v[cc], v[cc]));
+                        if (mode != LOCAL) {
+                            if (u & 1) acc1[cc] = fmaf(s[cc][k], qq[u], acc1[cc]); else acc0[cc] = fmaf(s[cc][k], qq[u], acc0[cc]);
+                        }
                     }
                 }
             }
             if (mode != LOCAL) {
-                float acc = acc0 + acc1;
 #pragma unroll
-                for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (live && r == 0) o_raw[(size_t)(tb + tok) * o_ld + h * vdim + j] = acc;
+                for (int cc = 0; cc < CPT; ++cc) {
+                    float acc = acc0[cc] + acc1[cc];
+#pragma unroll
+                    for (int o = R / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (live[cc] && r == 0) o_raw[(size_t)(tb + tok) * o_ld + h * vdim + j0 + jj + 32 * cc] = acc;
+                }
             }
         }
         __syncthreads();                                          // the tile may be overwritten
     }
     if (mode != FINAL) {
 #pragma unroll
-        for (int k = 0; k < ROWS; ++k)
-            if (live && i0 + k < dim) S[(size_t)(i0 + k) * vdim + j] = s[k];
+        for (int cc = 0; cc < CPT; ++cc)
+#pragma unroll
+            for (int k = 0; k < ROWS; ++k)
+                if (live[cc] && i0 + k < dim) S[(size_t)(i0 + k) * vdim + j0 + jj + 32 * cc] = s[cc][k];
     }
     if (mode == LOCAL && blockIdx.z == 0 && jj == 0) {
         float* G = piece_gates + ((size_t)blockIdx.x * heads + h) * dim;

@@ -50,7 +50,7 @@ def test_config_errors_name_the_key():
         (lambda c: c["layers"][0]["mlp"].update(kind="dense"), "kind"),
         (lambda c: c["layers"][0]["mlp"]["router"].update(top=9), "choices"),
         (lambda c: c["layers"][2].update(weights_of=2), "weights_of"),
-        (lambda c: c["layers"][1].update(weights_of=2), "weights_of"),
+        (lambda c: (c["layers"][0].update(weights_of=2), c["layers"][2].update(weights_of=0)), "weights_of"),
         (lambda c: c["norm"].pop("eps"), "eps"),
     ]
     for edit, word in cases:
@@ -110,3 +110,12 @@ def test_plain_chunks_and_groups():
     ids, weights, s = plain_lulisun.route(torch.ones(1, 3).double(), w, "", experts=4, top=2, groups=2, keep=1)
     assert sorted(ids[0].tolist()) == [0, 1]            # group 0: -5.9 beats group 1: -6.0, though expert 2 is the best
     assert torch.allclose(weights, torch.full((1, 2), 0.5).double())
+
+
+def test_shared_weights_may_be_named_through_another_sharer():
+    cfg = copy.deepcopy(lulisun_models.CONFIGS["B"])
+    cfg["layers"][0]["weights_of"] = 2             # 0 -> 2 -> 1: the owner is layer 1
+    typed = config_from_dict(cfg)
+    assert [L.weights_of for L in typed.layers] == [1, None, 1]
+    spec = get_architecture("Lulisun").build_spec(typed)
+    assert [e.layer for e in spec.schedule] == [0, 0, 0] and [e.cache for e in spec.schedule] == [0, 1, 2]
