@@ -1,11 +1,11 @@
 // Routed experts (a mixture of small gated feed-forward layers), on the device from the router to
 // the sum, so a step needs nothing from the host:
 //
-//   route     per token: z = W_router h in float32, s = sigmoid(z); choice score = s + correction;
-//             experts form `groups` equal groups of neighbours, a group's score is the sum of its
-//             two largest choice scores, only the `keep` best groups stay eligible (the others count
-//             as minus infinity); the `top` eligible experts with the largest choice scores are
-//             chosen; their weights are their plain scores s divided by the sum of those (+ 1e-20).
+//   route     per token: s = sigmoid(W_router h) in float32 and c = s + correction, which ranks the
+//             experts; expert e belongs to group e / (experts / groups); a group ranks by its top-2
+//             sum of c, and only the `keep` highest groups remain candidates (the rest leave the
+//             ranking, whatever the sign of their c); the `top` candidates with the highest c are
+//             taken, with weights s / (sum of the taken s + 1e-20).
 //             Optionally one more number per token: sigmoid(w_gate . h), the gate of a shared expert.
 //   arrange   the (token, choice) pairs listed expert by expert, cut into tiles of rows that belong
 //             to one expert
@@ -125,7 +125,7 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
     float* choice = score + experts;
     float* gscore = choice + experts;
 
-    // groups: the sum of a group's two largest choice scores; all but the `keep` best are shut out
+    // groups: top-2 sum of c per group; all but the `keep` highest leave the ranking
     const int size = experts / groups;
     if (keep < groups) {
         for (int g = lane; g < groups; g += 32) {

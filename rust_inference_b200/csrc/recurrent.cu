@@ -3,8 +3,8 @@
 //     S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T          S: [dim, vdim] per head, float32
 //     o_t = S_t^T q_t
 //
-// with q = silu(zq), f = low + (1 - low) * sigmoid(zf + bias): the forget gate also decides what is
-// written, there is no key.  The state lives in a per-slot area of the cache, starts at zero when a
+// with q = silu(zq), f = low + (1 - low) * sigmoid(zf + bias): the write weight 1 - f is tied to the forget
+// gate and takes a key's place.  The state lives in a per-slot area of the cache, starts at zero when a
 // slot is handed out and is carried from step to step, so a prompt may be cut anywhere and a decode
 // step is the same kernels with one token per sequence.  Everything here is float32: gates,
 // sigmoid, the state, the per-head RMS norm that follows.

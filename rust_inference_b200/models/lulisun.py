@@ -1,7 +1,7 @@
 """The Lulisun decoder as a `ModelSpec`.
 
 Every layer is x <- x + mixer(norm1(x)) + ff(norm2(x)) (`parallel_two_norms`), the norms RMS norms whose
-weight is stored around zero.  The mixer is two mixers side by side (`parallel_mixers`): grouped-query
+stored weight is an offset from one.  The mixer is two mixers on the same input (`parallel_mixers`): grouped-query
 softmax attention whose keys are limited to the query's own chunk of positions, with rotary positions
 on the first channels of every head, a value head size of its own and a score scale from the
 configuration; and a gated linear recurrence with a matrix state per head.  The feed-forward is a

@@ -12,7 +12,7 @@ from .spec import TensorSpec
 @register("norm", "rmsnorm")
 class RMSNorm(Norm):
     """y = x * (1 / sqrt(mean(x^2) + eps)) * weight; statistics in float32.  The weight
-    multiplies directly, unless `unit_offset` says that it is stored around zero: then the
+    multiplies directly, unless `unit_offset` says that the file holds weight - 1: then the
     factor is 1 + weight (formed once, in float32, when the weight arrives).  `weight_name` is
     the tensor's name below the part's prefix."""
 

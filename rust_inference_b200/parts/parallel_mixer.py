@@ -1,4 +1,4 @@
-"""Several mixers side by side on the same input, their results summed with fixed factors."""
+"""Several mixers on the same input, their results summed with fixed factors."""
 from __future__ import annotations
 
 from .base import Mixer
@@ -12,7 +12,7 @@ class ParallelMixers(Mixer):
     tensors sit below its spec's prefix, its factor is handed to it as `out_scale` (members apply it to
     their result in float32, before their output projection), and its cache is the member of the same
     place in the layer's composite cache request: an attention member keeps keys and values, a
-    recurrent one a state, side by side in one cache layer."""
+    recurrent one a state, both in one cache layer."""
 
     def __init__(self, *, members, hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)

@@ -18,8 +18,8 @@ class GatedLinearRecurrence(Mixer):
         q = silu(Wq x)            f = low + (1 - low) * sigmoid(Wf x + b)        v = Wv x
         S <- diag(f) S + (1 - f) v^T          o = S^T q
 
-    The forget gate f (bounded below by `low`, per head and channel) also decides what is written;
-    there is no key.  Every head's o is RMS-normed over vdim with one weight shared by the heads,
+    The forget gate f lies in [low, 1) per head and channel, and the write is tied to it (weight 1 - f),
+    which takes the place of a key.  Every head's o is RMS-normed over vdim with one weight shared by the heads,
     the heads are concatenated and projected by Wo onto the residual stream.  The three projections
     run as one product with float32 results; gates, state and norm are float32 in both precisions.
     `out_scale` multiplies the mixer's result (applied to the normed o, in float32).  `names` gives

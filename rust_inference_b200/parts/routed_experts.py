@@ -13,10 +13,10 @@ from .spec import TensorSpec
 class RoutedExperts(FeedForward):
     """`n_experts` experts of the form down(silu(gate x) * (up x)), of which every token uses `top`.
 
-    Router: s = sigmoid(W_router x) in float32.  The choice is made on s + correction, limited to the
-    `group_keep` best of `n_groups` equal groups of neighbouring experts (a group's score is the sum of
-    its two largest choice scores; the other groups' experts count as minus infinity).  The chosen
-    experts' results are weighted by their s divided by the sum of those (+ 1e-20).  A shared expert of
+    Router: s = sigmoid(W_router x) in float32; c = s + correction ranks the experts.  Experts e with the same
+    e // (n_experts / n_groups) form a group, ranked by its top-2 sum of c; only the `group_keep` highest groups
+    remain candidates (the rest are removed from the ranking, whatever the sign of their c).  The `top`
+    candidates with the highest c run, weighted by s / (sum of the chosen s + 1e-20).  A shared expert of
     width `shared_size` (None: none) runs for every token and is added times sigmoid(w_sg . x).
 
     Everything from the router to the sum runs on the device (`csrc/moe.cu`), so decode steps stay

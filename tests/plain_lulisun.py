@@ -1,5 +1,5 @@
-"""A plain, slow restatement of the Lulisun decoder, one function per mechanism, written from the
-design's equations and sharing nothing with the library: whole sequences at once, no cache, no
+"""A plain, slow restatement of the Lulisun decoder, one function per mechanism, written from its
+equations and sharing nothing with the library: whole sequences at once, no cache, no
 batching, float64 unless told otherwise.  Tests compare the engine with it.
 
 Notation: x_t is the stream at token t (width D), h the normalised input of a block.  A layer is
@@ -15,7 +15,7 @@ import torch
 
 
 def unit_offset_rmsnorm(x, w, eps):
-    """x / sqrt(mean(x^2) + eps) * (1 + w): the stored weight lies around zero."""
+    """x / sqrt(mean(x^2) + eps) * (1 + w): the file holds the factor minus one."""
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * (1.0 + w)
 
 
@@ -87,9 +87,9 @@ def gated_expert(h, w, pre):
 
 
 def route(h, w, pre, *, experts, top, groups, keep):
-    """Which experts each token uses and with what weights: sigmoid scores; the choice adds a
-    correction and is limited to the `keep` groups whose two best choice scores sum highest;
-    the weights are the plain scores of the chosen, normalised."""
+    """ids [T, top] and weights [T, top]: s = sigmoid(router h); c = s + correction ranks; groups of
+    experts / groups consecutive experts rank by their top-2 sum of c and only the `keep` highest stay in
+    the ranking; the `top` highest c are taken with weights s / sum(s of the taken)."""
     s = torch.sigmoid(h @ w[pre + "router"].T)                          # [T, E]
     choice = s + w[pre + "correction"]
     n = h.shape[0]

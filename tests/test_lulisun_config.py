@@ -59,7 +59,7 @@ def test_config_errors_name_the_key():
 
 
 def test_cache_layers_of_a_parallel_mixer():
-    """Every layer run gets keys and values (values with their own head size) and a state, side by side;
+    """Every layer run gets keys and values (values with their own head size) and a state, together;
     layers with the same needs share a storage group."""
     from rust_inference_b200.cache.sequence_cache import CompositeLayer, KVRequest, SequenceCache, StateRequest
     from rust_inference_b200.engine.model import DecoderModel

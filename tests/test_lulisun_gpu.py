@@ -29,11 +29,11 @@ def d(t, dtype=None):
 # ---------------------------------------------------------------------------------------------------
 # mechanisms alone
 # ---------------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("experts,top,groups,keep", [(12, 3, 3, 2), (16, 2, 2, 1), (6, 2, 6, 3), (5, 1, 1, 1), (64, 6, 8, 3)])
+@pytest.mark.parametrize("experts,top,groups,keep", [(12, 3, 3, 2), (16, 3, 4, 2), (6, 2, 6, 3), (5, 1, 1, 1), (64, 6, 8, 3)])
 @pytest.mark.parametrize("negative", [False, True])
 def test_router_choice_and_weights(experts, top, groups, keep, negative):
     """ids and weights of the route kernel equal the plain router's; with `negative` all choice scores lie
-    below zero, where an excluded group counted as 0 instead of minus infinity would win."""
+    below zero, where a removed group whose scores were merely zeroed would win."""
     from rust_inference_b200.kernels import ops
     g = torch.Generator().manual_seed(experts * 7 + top)
     n, width = 37, 48
@@ -143,7 +143,7 @@ def test_grouped_expert_products_on_tensor_cores(experts, top, ff, width, n):
 
 
 @pytest.mark.parametrize("lens,cuts", [([23, 9], (100, 5, 2, 1, 100)), ([333, 150], (1000, 140, 64, 1000))])
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 48, 32), (1, 72, 33), (3, 24, 40), (2, 8, 16), (1, 130, 70), (1, 300, 8)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 40, 24), (1, 72, 33), (3, 24, 40), (2, 8, 16), (1, 130, 70), (1, 300, 8)])
 def test_recurrence_in_portions_and_slots(heads, dim, vdim, lens, cuts):
     """The recurrence kernel over a whole sequence, and cut into portions of 1, 2 and 5 tokens with the
     state carried in the slot, for two sequences of unequal length in one call; then the slots are used
@@ -239,7 +239,7 @@ def test_chunk_edges_with_one_key_that_stands_out(dtype):
 
 
 @pytest.mark.parametrize("hd", [64, 128])
-@pytest.mark.parametrize("chunk", [7, 64, 100, 200])
+@pytest.mark.parametrize("chunk", [7, 64, 100, 160])
 def test_chunked_attention_on_tensor_cores(hd, chunk):
     """The tensor-core kernels (tcgen05 prefill, split decode) with a chunk mask and an output factor against
     the generic kernel on the same cache: continuations that start inside a chunk, query tiles that span
@@ -519,3 +519,51 @@ def test_trace_replay_picks_the_model_by_its_config(models, tmp_path):
     for i in range(4):
         got = torch.from_numpy(np.fromfile(out / f"{i + 1}.f32", dtype="<f4").reshape(1, -1))
         assert rel_err(got, want[66 + i:67 + i]) < TOL["float32"]
+
+
+def test_checked_build_stays_silent_and_skips_a_bad_slot(tmp_path):
+    """The checked build (indices that reach memory through a table are compared with their limits) runs a
+    Lulisun model in both precisions without a record; the recurrence kernel handed a slot beyond the
+    cache's slots records it and leaves state and output alone.  In a process of its own: the build is
+    chosen when the package is imported."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = textwrap.dedent("""
+        import sys, pathlib, tempfile, torch
+        sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+        import lulisun_models
+        from conftest import random_tokens, rel_err
+        from rust_inference_b200.engine.engine import Engine
+        from rust_inference_b200.kernels import build, ops
+        assert build.CHECKED and build.library_path("recurrent").endswith("checked/libri_recurrent.so")
+        model = lulisun_models.make(pathlib.Path(tempfile.mkdtemp()), "B", pinned=True)
+        toks = random_tokens(150, model.cfg["vocab"], 3)
+        want = model.plain_logits(toks)
+        for dtype in ("float32", "bfloat16"):
+            eng = Engine.from_pretrained(model.folder, dtype=dtype, max_tokens=512, n_slots=3)
+            s = eng.alloc_slot()
+            head = eng.step([s], [toks[:140]], "all").cpu()
+            tail = torch.cat([eng.step([s], [[t]], "last").cpu() for t in toks[140:]])
+            assert rel_err(torch.cat([head, tail]), want) <= (1e-4 if dtype == "float32" else 8e-2)
+            eng.check_device_status()
+        assert ops.bounds_report() == []
+        heads, dim, vdim = 2, 8, 16
+        z = torch.randn(1, 2 * heads * dim + heads * vdim, device="cuda")
+        state = torch.full((3, heads, dim, vdim), 5.0, device="cuda")
+        out = torch.full((1, heads * vdim), 7.0, device="cuda")
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+        ops.gated_recurrence(z, torch.zeros(heads * dim, device="cuda"), torch.zeros(heads * dim, device="cuda"),
+                             torch.ones(vdim, device="cuda"), state, i32([0, 1]), i32([9]), out, n_seqs=1, heads=heads,
+                             dim=dim, vdim=vdim, eps=1e-5, longest_run=1)
+        torch.cuda.synchronize()
+        assert float((state - 5.0).abs().max()) == 0.0
+        rep = ops.bounds_report()
+        assert rep and rep[0][0] == "recurrent" and rep[0][1] == "a cache slot that does not exist" and rep[0][2] == 9, rep
+        print("checked ok")
+    """).format(root=root, tests=os.path.join(root, "tests"))
+    env = dict(os.environ, RI_B200_CHECK_BOUNDS="1")
+    p = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0 and "checked ok" in p.stdout, p.stderr[-3000:]
