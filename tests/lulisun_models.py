@@ -57,15 +57,21 @@ CONFIGS = {
 
 
 def pin_routing(cfg, weights):
-    """Corrections 1.5 apart: the order of the choice scores no longer hangs on the router's sigmoid, so a
-    bfloat16 run and the plain one choose the same experts at every token (the weights of the chosen
-    still come from the router)."""
+    """Corrections that decide the choice by themselves: 1.5 apart within a group of experts and 20 apart
+    from group to group, so neither the order of the groups' top-2 sums nor the order of the experts hangs
+    on the router's sigmoid (which lies in (0, 1)), and a bfloat16 run and the plain one choose the same
+    experts at every token (the weights of the chosen still come from the router)."""
     out = dict(weights)
     for i, layer in enumerate(cfg["layers"]):
         if layer.get("weights_of") is None and layer.get("mlp") is not None:
-            n = layer["mlp"]["router"]["experts"]
-            perm = torch.randperm(n, generator=torch.Generator().manual_seed(i))
-            out[f"l{i}.mlp.correction"] = (perm.float() * 1.5 - 4.0).to(torch.bfloat16)
+            router = layer["mlp"]["router"]
+            n = router["experts"]
+            groups = (router.get("groups") or {"count": 1})["count"]
+            size = n // groups
+            g = torch.Generator().manual_seed(i)
+            group_rank = torch.randperm(groups, generator=g).float()
+            c = torch.cat([20.0 * group_rank[k] + 1.5 * torch.randperm(size, generator=g).float() for k in range(groups)])
+            out[f"l{i}.mlp.correction"] = (c - 8.0).to(torch.bfloat16)
     return out
 
 
