@@ -274,6 +274,14 @@ def test_chunked_attention_on_tensor_cores(hd, chunk):
         ops.attention_generic(qkv, qkv.shape[1], kc, vc, ctx.page_table, ctx.token_pos, ctx.token_seq, ctx.seq_slot, plain,
                               n_tokens=n, n_heads=heads, n_kv_heads=kvh, head_dim=hd, page_size=page, scale=0.11, chunk=chunk,
                               out_scale=0.7)
+        if not ctx.all_single:
+            # the mma.sync prefill kernel (what runs where the tcgen05 one does not take the row strides)
+            other = torch.empty(n, heads * hd, dtype=bf, device=DEV)
+            ops.attention_prefill(qkv, qkv.shape[1], kc, vc, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens, other,
+                                  n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=heads, n_kv_heads=kvh, head_dim=hd,
+                                  page_size=page, scale=0.11, window=-chunk)
+            ops.scale_(other, 0.7)
+            assert rel_err(other, plain) < 2e-2, (starts, news, "mma")
         torch.cuda.synchronize()
         from rust_inference_b200.kernels import tcgen05
         tcgen05.check_status()
