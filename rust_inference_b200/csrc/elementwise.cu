@@ -217,6 +217,66 @@ RI_API int ri_rmsnorm(const float* x, const float* w, const int* rows, void* out
     return check_launch(e, "rmsnorm");
 }
 
+// Two norms of the same rows with one pass over the statistics: out_a = x / rms * w_a, out_b = x / rms * w_b
+// (a layer whose mixer and feed-forward read the same stream through norms of their own).  For steps of few
+// rows, where a kernel's launch costs more than its work; a block per row.
+namespace {
+template <typename T>
+__global__ void rmsnorm_pair_kernel(const float* x, const float* __restrict__ w_a, const float* __restrict__ w_b,
+                                    T* __restrict__ out_a, T* __restrict__ out_b, int n, float eps, int vec) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // x is the residual stream the previous kernel wrote
+    const float* xr = x + (size_t)r * n;
+    float ss = 0.f;
+    if (vec) {
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    T* oa = out_a + (size_t)r * n;
+    T* ob = out_b + (size_t)r * n;
+    if (vec) {
+        for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            const float4 a = reinterpret_cast<const float4*>(w_a)[i], b = reinterpret_cast<const float4*>(w_b)[i];
+            store4<T>(oa + 4 * i, v.x * scale * a.x, v.y * scale * a.y, v.z * scale * a.z, v.w * scale * a.w);
+            store4<T>(ob + 4 * i, v.x * scale * b.x, v.y * scale * b.y, v.z * scale * b.z, v.w * scale * b.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = xr[i] * scale;
+            oa[i] = from_f32<T>(v * w_a[i]);
+            ob[i] = from_f32<T>(v * w_b[i]);
+        }
+    }
+}
+}  // namespace
+
+RI_API int ri_rmsnorm_pair(const float* x, const float* w_a, const float* w_b, void* out_a, void* out_b, int out_dtype,
+                           int n_rows, int n, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int vec = n % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w_a % 16 == 0 && (uintptr_t)w_b % 16 == 0 &&
+                    (uintptr_t)out_a % 16 == 0 && (uintptr_t)out_b % 16 == 0;
+    int threads = vec ? ((n / 4 + 31) / 32) * 32 : 256;
+    threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : threads);
+    cudaError_t e;
+    if (out_dtype == RI_F32)
+        e = launch_dependent(rmsnorm_pair_kernel<float>, n_rows, threads, 0, stream, x, w_a, w_b, (float*)out_a, (float*)out_b, n, eps, vec);
+    else if (out_dtype == RI_BF16)
+        e = launch_dependent(rmsnorm_pair_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w_a, w_b, (__nv_bfloat16*)out_a,
+                             (__nv_bfloat16*)out_b, n, eps, vec);
+    else
+        return fail("rmsnorm_pair: unknown dtype %d", out_dtype);
+    return check_launch(e, "rmsnorm_pair");
+}
+
 // ----------------------------------------------------------------------------
 // Rotary position encoding + cache write.
 //

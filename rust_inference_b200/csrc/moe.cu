@@ -45,7 +45,7 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
-constexpr int ROUTE_WARPS = 16;
+constexpr int ROUTE_WARPS = 32;
 constexpr int ROUTE_TOKENS = 8;           // most tokens a block routes: the router's rows are read once for all of them
 
 template <typename T> __device__ __forceinline__ void load4_f32(const T* p, float* o);
@@ -184,7 +184,8 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
 // pairs of one expert; n_tiles[0] their number; place[p] (optional) the index of pair p in `order`.
 __global__ void __launch_bounds__(1024)
 moe_arrange_kernel(const int* ids, int n_pairs, int experts, int tile_rows, int* __restrict__ offsets,
-                   int* __restrict__ order, int* __restrict__ tiles, int* __restrict__ n_tiles, int* __restrict__ place) {
+                   int* order, int* __restrict__ tiles, int* __restrict__ n_tiles, int* __restrict__ place,
+                   const uint4* x, uint4* __restrict__ xs, int top, int vecs) {
     extern __shared__ int sh[];
     int* count = sh;                 // [experts]
     int* start = sh + experts;       // [experts + 1]
@@ -222,6 +223,14 @@ moe_arrange_kernel(const int* ids, int n_pairs, int experts, int tile_rows, int*
             const int at = start[e] + atomicAdd(&fill[e], 1);
             order[at] = p;
             if (place != nullptr) place[p] = at;
+        }
+    }
+    if (xs != nullptr) {
+        // a step of few pairs: the activations go into the lists' order here, without a kernel of their own
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_pairs * vecs; i += blockDim.x) {
+            const int r = i / vecs, c = i % vecs;
+            xs[i] = x[(size_t)(order[r] / top) * vecs + c];
         }
     }
 }
@@ -365,14 +374,17 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
 
 RI_API int ri_moe_tile_rows() { return GM; }
 
+// x, xs (optional, bf16 rows of `width` values, a multiple of 8): also xs[i] = x[order[i] / top], for steps of few pairs.
 RI_API int ri_moe_arrange(const int* ids, int n_pairs, int experts, int tile_rows, int* offsets, int* order, int* tiles,
-                          int* n_tiles, int* place, cudaStream_t stream) {
+                          int* n_tiles, int* place, const void* x, void* xs, int top, int width, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (tile_rows <= 0) return fail("moe_arrange: tile of %d rows", tile_rows);
     const size_t smem = (size_t)(3 * experts + 1) * sizeof(int);
     if (smem > 48 * 1024) return fail("moe_arrange: %d experts exceed the kernel's shared memory", experts);
+    if (xs != nullptr && (x == nullptr || top <= 0 || width % 8 || (uintptr_t)x % 16 || (uintptr_t)xs % 16))
+        return fail("moe_arrange: rows of %d bf16 cannot be gathered 16 bytes at a time", width);
     cudaError_t e = launch_dependent(moe_arrange_kernel, 1, 1024, smem, stream, ids, n_pairs, experts, tile_rows, offsets,
-                                     order, tiles, n_tiles, place);
+                                     order, tiles, n_tiles, place, (const uint4*)x, (uint4*)xs, top, width / 8);
     return check_launch(e, "moe_arrange");
 }
 

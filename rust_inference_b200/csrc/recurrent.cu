@@ -11,6 +11,7 @@
 //
 // Three kernels, all reading the step's arrays on the device (graph-safe):
 //   prepare  zq <- silu(zq), zf <- low + (1 - low) sigmoid(zf + bias), in place, every token at once
+//            (long runs only: the one-pass scan of a decode step or a short portion does it in its tile)
 //   scan     per (sequence, head, tile of value columns): the recurrence over the sequence's new
 //            tokens in order; the state is read first and written last.  Long runs of new tokens are
 //            cut into pieces that are scanned side by side (see below), all in float32
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(SCAN_THREADS)
 recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float* state,
                        float* piece_state, float* piece_gates, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ seq_slot, int heads, int dim, int vdim, int piece, int max_pieces,
-                       int tile_t) {
+                       int tile_t, const float* __restrict__ prep_bias, const float* __restrict__ prep_low) {
     using Tile = ScanTile<ROWS>;
     extern __shared__ __align__(16) float tile[];
     const int b = blockIdx.x / max_pieces, c = blockIdx.x % max_pieces, h = blockIdx.y;
@@ -158,6 +159,22 @@ recurrence_scan_kernel(const float* z, int ld, float* __restrict__ o_raw, float*
             }
         }
         __syncthreads();
+        if (mode == WHOLE && prep_bias != nullptr) {
+            // the one-pass form applies the activations itself (no kernel of its own for a step's few tokens):
+            // f <- low + (1 - low) sigmoid(f + bias), q <- silu(q), in the tile
+            for (int idx = threadIdx.x; idx < n_tok * 2 * dim; idx += SCAN_THREADS) {
+                const int tok = idx / (2 * dim), it = idx % (2 * dim);
+                const int ch = it < dim ? it : it - dim;
+                float* at = tile + tok * Tile::TOKEN + (it < dim ? 0 : R * Tile::SLICE) + (ch / ROWS) * Tile::SLICE + ch % ROWS;
+                if (it < dim) {
+                    const float l = prep_low[h * dim + ch];
+                    *at = l + (1.f - l) * sigmoid_f32(*at + prep_bias[h * dim + ch]);
+                } else {
+                    *at = silu_f32(*at);
+                }
+            }
+            __syncthreads();
+        }
         // ---- the recurrence over the tile, out of shared memory ----
         for (int tok = 0; tok < n_tok; ++tok) {
             const float* base = tile + tok * Tile::TOKEN;
@@ -265,7 +282,7 @@ constexpr int SCAN_SMEM_LIMIT = 96 * 1024;       // two blocks to an SM
 template <int ROWS>
 int launch_scan(bool vec, dim3 grid, cudaStream_t stream, const float* z, int ld, float* o_raw, float* state,
                 float* piece_state, float* piece_gates, const int* cu_seqlens, const int* seq_slot, int heads, int dim,
-                int vdim, int mode, int piece, int max_pieces, int longest) {
+                int vdim, int mode, int piece, int max_pieces, int longest, const float* prep_bias, const float* prep_low) {
     const int token_bytes = ScanTile<ROWS>::TOKEN * (int)sizeof(float);
     int tile_t = SCAN_SMEM_LIMIT / token_bytes;
     if (tile_t > 64) tile_t = 64;
@@ -279,7 +296,7 @@ int launch_scan(bool vec, dim3 grid, cudaStream_t stream, const float* z, int ld
         static PerDeviceOnce once;                                                                                        \
         if (int rc = raise_dynamic_smem(kernel, SCAN_SMEM_LIMIT, once, "gated_recurrence")) return rc;                    \
         e = launch_dependent(kernel, grid, SCAN_THREADS, smem, stream, z, ld, o_raw, state, piece_state, piece_gates,     \
-                             cu_seqlens, seq_slot, heads, dim, vdim, piece, max_pieces, tile_t);                          \
+                             cu_seqlens, seq_slot, heads, dim, vdim, piece, max_pieces, tile_t, prep_bias, prep_low);     \
     }
     if (vec) {
         if (mode == WHOLE) RI_LAUNCH(true, WHOLE) else if (mode == LOCAL) RI_LAUNCH(true, LOCAL) else RI_LAUNCH(true, FINAL)
@@ -297,8 +314,8 @@ RI_API long long ri_gated_recurrence_scratch(int n_seqs, int max_pieces, int hea
     return (long long)n_seqs * max_pieces * heads * dim * ((long long)vdim + 1);
 }
 
-// z: float32 [n_tokens, ld] = [zq (heads*dim) | zf (heads*dim) | v (heads*vdim)]; zq and zf are overwritten
-// by q and f.  o_raw: float32 [n_tokens, heads*vdim] scratch.  state: float32 [slots, heads, dim, vdim].
+// z: float32 [n_tokens, ld] = [zq (heads*dim) | zf (heads*dim) | v (heads*vdim)]; with pieces zq and zf are
+// overwritten by q and f.  o_raw: float32 [n_tokens, heads*vdim] scratch.  state: float32 [slots, heads, dim, vdim].
 // out: [n_tokens, heads*vdim] in `dtype`.  piece > 0: sequences' new tokens are cut into pieces of that many
 // tokens, at most max_pieces per sequence (the longest run of new tokens / piece, rounded up), worked on side
 // by side with `scratch` (ri_gated_recurrence_scratch floats); piece == 0: one pass per sequence.
@@ -315,7 +332,7 @@ RI_API int ri_gated_recurrence(float* z, int ld, const float* bias, const float*
     if (dim > 64 * R) return fail("gated_recurrence: a head of %d channels exceeds %d", dim, 64 * R);
     if (piece > 0 && (max_pieces <= 0 || scratch == nullptr)) return fail("gated_recurrence: pieces need scratch");
     const int qdim = heads * dim;
-    {
+    if (piece > 0) {                      // the one-pass scan applies the activations itself
         const size_t total = (size_t)n_tokens * qdim;
         const int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
         cudaError_t e = launch_dependent(recurrence_prepare_kernel, blocks, 256, 0, stream, z, ld, bias, low, n_tokens, qdim);
@@ -330,7 +347,8 @@ RI_API int ri_gated_recurrence(float* z, int ld, const float* bias, const float*
         dim3 grid(n_seqs * mp, heads, col_tiles);
         const int longest = mode == WHOLE ? (longest_run > 0 ? longest_run : n_tokens) : piece;
 #define RI_SCAN(ROWS) launch_scan<ROWS>(vec, grid, stream, z, ld, o_raw, state, piece_state, piece_gates, cu_seqlens, seq_slot, \
-                                        heads, dim, vdim, mode, piece > 0 ? piece : 1, mp, longest)
+                                        heads, dim, vdim, mode, piece > 0 ? piece : 1, mp, longest,                         \
+                                        mode == WHOLE ? bias : nullptr, mode == WHOLE ? low : nullptr)
         if (rows == 4) return RI_SCAN(4);
         if (rows == 8) return RI_SCAN(8);
         if (rows == 16) return RI_SCAN(16);

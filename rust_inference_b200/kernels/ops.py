@@ -190,6 +190,21 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
+def rmsnorm_pair(x: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float, out_a: torch.Tensor,
+                 out_b: torch.Tensor) -> None:
+    """out_a = rmsnorm(x) * weight_a and out_b = rmsnorm(x) * weight_b of the same rows with one pass over the
+    statistics.  x and the weights float32; the outputs float32 or bfloat16, [R, n] each."""
+    _need_cuda(x, weight_a, weight_b, out_a, out_b)
+    n_rows, n = out_a.shape
+    _need(x.dtype == torch.float32 and weight_a.dtype == torch.float32 and weight_b.dtype == torch.float32
+          and x.is_contiguous() and x.shape[-1] == n and x.shape[0] >= n_rows and weight_a.numel() == n
+          and weight_b.numel() == n, "rmsnorm_pair: x and the weights must be float32 [.., n]")
+    _need(out_b.shape == out_a.shape and out_b.dtype == out_a.dtype and out_a.is_contiguous() and out_b.is_contiguous(),
+          "rmsnorm_pair: two outputs of one shape and dtype")
+    _call("elementwise", "ri_rmsnorm_pair", _p(x), _p(weight_a), _p(weight_b), _p(out_a), _p(out_b),
+          c_int(dtype_code(out_a.dtype)), c_int(n_rows), c_int(n), c_float(eps), _stream())
+
+
 def rope_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_pos, token_seq,
                      seq_slot, page_table: torch.Tensor, kcache, vcache, *, n_heads: int,
                      n_kv_heads: int, head_dim: int, page_size: int, style: int, write_kv: bool,
@@ -493,7 +508,7 @@ def gated_recurrence(z: torch.Tensor, bias: torch.Tensor, lower: torch.Tensor, n
           c_int(heads), c_int(dim), c_int(vdim), c_float(eps), c_float(out_scale), c_int(piece), c_int(max_pieces),
           _p(scratch if piece > 0 else None), c_int(max(0, min(int(longest_run), n))), _stream())
     global _launches
-    _launches += 4 if piece > 0 else 2                    # several kernels behind one entry point
+    _launches += 4 if piece > 0 else 1                    # several kernels behind one entry point
     return out
 
 
@@ -528,18 +543,28 @@ def moe_tile_rows() -> int:
 
 
 def moe_arrange(ids: torch.Tensor, n_pairs: int, experts: int, tile_rows: int, offsets: torch.Tensor,
-                order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor, place: torch.Tensor | None = None) -> None:
+                order: torch.Tensor, tiles: torch.Tensor, n_tiles: torch.Tensor, place: torch.Tensor | None = None,
+                gather: tuple | None = None) -> None:
     """The (token, choice) pairs listed expert by expert (`offsets` int32 [experts + 1] into `order` int32
     [pairs]) and cut into tiles of at most tile_rows pairs of one expert (`tiles` int32 [2 * (pairs /
     tile_rows + experts)]: expert and first index; `n_tiles` int32 [1]).  `place` int32 [pairs]: where in
-    `order` each pair stands."""
+    `order` each pair stands.  `gather` = (x, xs, top): the kernel also copies the activations into the
+    lists' order, xs[i] = x[order[i] // top] (as `moe_gather` does; for steps of few pairs)."""
     _need_cuda(ids, offsets, order, tiles, n_tiles, place)
     for t in (ids, offsets, order, tiles, n_tiles, place):
         _need(t is None or (t.dtype == torch.int32 and t.is_contiguous()), "moe_arrange: int32 arrays")
     _need(offsets.numel() >= experts + 1 and order.numel() >= n_pairs and (place is None or place.numel() >= n_pairs)
           and tiles.numel() >= 2 * (-(-n_pairs // tile_rows) + experts), "moe_arrange: arrays too small")
+    x = xs = None
+    top = width = 0
+    if gather is not None:
+        x, xs, top = gather
+        _need_cuda(x, xs)
+        width = x.shape[1]
+        _need(x.dtype == torch.bfloat16 and xs.dtype == torch.bfloat16 and x.is_contiguous() and xs.is_contiguous()
+              and xs.shape == (n_pairs, width) and x.shape[0] * top >= n_pairs and width % 8 == 0, "moe_arrange: gather shapes")
     _call("moe", "ri_moe_arrange", _p(ids), c_int(n_pairs), c_int(experts), c_int(tile_rows), _p(offsets), _p(order),
-          _p(tiles), _p(n_tiles), _p(place), _stream())
+          _p(tiles), _p(n_tiles), _p(place), _p(x), _p(xs), c_int(top), c_int(width), _stream())
 
 
 def moe_gather(x: torch.Tensor, xs: torch.Tensor, order: torch.Tensor, *, n_pairs: int, top: int) -> torch.Tensor:

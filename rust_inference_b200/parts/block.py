@@ -32,11 +32,15 @@ class ParallelTwoNorms(Arrangement):
     def forward(self, residual, ctx, cache_layer, writes_cache):
         shape = (residual.shape[0], residual.shape[1])
         normed = ctx.buffer("normed", shape, ctx.dtype)
-        self.mixer_norm.forward(residual, normed)
         if self.feed_forward is not None:
-            # both norms read the stream before either branch adds to it
+            # both norms read the stream before either branch adds to it (small steps: one kernel for the two)
             normed_ff = ctx.buffer("normed_ff", shape, ctx.dtype)
-            self.feed_forward_norm.forward(residual, normed_ff)
+            pair = getattr(self.mixer_norm, "forward_with", None)
+            if pair is None or not pair(self.feed_forward_norm, residual, normed, normed_ff):
+                self.mixer_norm.forward(residual, normed)
+                self.feed_forward_norm.forward(residual, normed_ff)
+        else:
+            self.mixer_norm.forward(residual, normed)
         self.mixer.forward(normed, residual, ctx, cache_layer, writes_cache)
         if self.feed_forward is not None:
             self.feed_forward.forward(normed_ff, residual, ctx)

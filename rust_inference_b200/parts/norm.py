@@ -37,3 +37,14 @@ class RMSNorm(Norm):
 
     def forward(self, x, out, rows=None):
         return ops.rmsnorm(x, self.factor, self.eps, out, rows)
+
+    # up to so many rows two norms of the same stream run as one kernel (a launch costs more than the rows)
+    PAIR_MAX_ROWS = 128
+
+    def forward_with(self, other, x, out, out_other) -> bool:
+        """out = self(x) and out_other = other(x) in one kernel, if `other` is an RMS norm with the same eps
+        and the step is small; False (nothing done) otherwise."""
+        if not isinstance(other, RMSNorm) or other.eps != self.eps or out.shape[0] > self.PAIR_MAX_ROWS:
+            return False
+        ops.rmsnorm_pair(x, self.factor, other.factor, self.eps, out, out_other)
+        return True

@@ -87,6 +87,7 @@ class RoutedExperts(FeedForward):
     # expert, their weights streamed by TMA) when the sizes allow; the FFMA form is the 32-bit path and
     # the fallback for other sizes
     TENSOR_CORE_MIN_TOKENS = 0
+    GATHER_IN_ARRANGE_PAIRS = 256       # up to so many (token, choice) pairs the arranging block also gathers their rows
 
     def _on_tensor_cores(self, x) -> bool:
         if x.dtype != torch.bfloat16 or x.shape[0] <= self.TENSOR_CORE_MIN_TOKENS:
@@ -114,13 +115,17 @@ class RoutedExperts(FeedForward):
         tiles = ctx.buffer("moe_tiles", (2 * (-(-pairs // rows) + experts),), torch.int32)
         n_tiles = ctx.buffer("moe_n_tiles", (1,), torch.int32)
         place = ctx.buffer("moe_place", (pairs,), torch.int32) if fast else None
-        ops.moe_arrange(ids, pairs, experts, rows, offsets, order, tiles, n_tiles, place)
+        # an expert's rows consecutive: the activations are gathered into the lists' order (by the arranging
+        # kernel itself when the pairs are few); act and y stay in that order
+        xs = ctx.buffer("moe_x_sorted", (pairs, h), self.dtype) if fast else None
+        small = fast and pairs <= self.GATHER_IN_ARRANGE_PAIRS
+        ops.moe_arrange(ids, pairs, experts, rows, offsets, order, tiles, n_tiles, place,
+                        gather=(x, xs, top) if small else None)
         act = ctx.buffer("moe_act", (pairs, self.expert_size), self.dtype)
         y = ctx.buffer("moe_y", (pairs, h), torch.float32)
         if fast:
-            # an expert's rows consecutive: gather the activations into the lists' order; act and y stay in it
-            xs = ctx.buffer("moe_x_sorted", (pairs, h), self.dtype)
-            ops.moe_gather(x, xs, order, n_pairs=pairs, top=top)
+            if not small:
+                ops.moe_gather(x, xs, order, n_pairs=pairs, top=top)
             tcgen05.grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, n_tiles, n_pairs=pairs)
             tcgen05.grouped_gemm(act, self.w_down, None, y, offsets, tiles, n_tiles, n_pairs=pairs)
         else:

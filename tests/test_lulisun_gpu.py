@@ -124,6 +124,11 @@ def test_grouped_expert_products_on_tensor_cores(experts, top, ff, width, n):
     xs = torch.empty(pairs, width, dtype=bf, device=DEV)
     ops.moe_gather(d(x), xs, order, n_pairs=pairs, top=top)
     assert torch.equal(xs.cpu(), x[(order.cpu().long() // top)])
+    if pairs <= 256:                                  # few pairs: the arranging kernel gathers the rows itself
+        xs2 = torch.empty_like(xs)
+        ops.moe_arrange(d(ids), pairs, experts, rows, offsets, order, tiles, n_tiles, place, gather=(d(x), xs2, top))
+        assert torch.equal(xs2.cpu(), x[(order.cpu().long() // top)])
+        xs = xs2
     act = torch.full((pairs, ff), float("nan"), dtype=bf, device=DEV)
     tcgen05.grouped_gemm(xs, wg_d, wu_d, act, offsets, tiles, n_tiles, n_pairs=pairs)
     y = torch.full((pairs, width), float("nan"), dtype=torch.float32, device=DEV)
@@ -291,6 +296,20 @@ def test_chunked_attention_on_tensor_cores(hd, chunk):
     run([chunk - 1, chunk, min(3 * chunk - 1, 440)], [130, 2, 64])        # every sequence stays within its 8 pages
     for base in (chunk - 1, chunk, chunk + 1, 2 * chunk, 200, 449):
         run([base, base + 1, max(0, base - 1)], [1, 1, 1])     # decode steps around a chunk's first position
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,n", [(1, 72), (8, 2048), (37, 100), (128, 4096)])
+def test_two_norms_in_one_kernel(dtype, rows, n):
+    from rust_inference_b200.kernels import ops
+    g = torch.Generator().manual_seed(n)
+    x = torch.randn(rows, n, generator=g) * 3
+    wa, wb = 1 + torch.randn(n, generator=g) * 0.2, 1 + torch.randn(n, generator=g) * 0.2
+    a, b = torch.empty(rows, n, dtype=dtype, device=DEV), torch.empty(rows, n, dtype=dtype, device=DEV)
+    ops.rmsnorm_pair(d(x), d(wa), d(wb), 1e-5, a, b)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert rel_err(a, plain_lulisun.plain_rmsnorm(x.double(), wa.double(), 1e-5)) < tol
+    assert rel_err(b, plain_lulisun.plain_rmsnorm(x.double(), wb.double(), 1e-5)) < tol
 
 
 def test_partial_rotation_and_value_cache():
