@@ -19,7 +19,7 @@ from ..config.registry import register_architecture
 from ..parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 # the configuration gives no context length: positions are bounded by the cache a run is given
-MAX_POSITIONS = 1 << 20
+MAX_POSITIONS = 1 << 17
 
 _ATTENTION_NAMES = {"q": "q", "k": "k", "v": "v", "o": "o"}
 _RECURRENCE_NAMES = {"q": "q", "f": "f", "f_bias": "f.b", "lower": "lower", "v": "v", "norm": "norm", "o": "o"}

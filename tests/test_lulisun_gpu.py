@@ -594,3 +594,30 @@ def test_checked_build_stays_silent_and_skips_a_bad_slot(tmp_path):
     env = dict(os.environ, RI_B200_CHECK_BOUNDS="1")
     p = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=900)
     assert p.returncode == 0 and "checked ok" in p.stdout, p.stderr[-3000:]
+
+
+def test_the_command_line_on_a_lulisun_folder(models, tmp_path):
+    """`bin/gguf-infer` as a process: greedy ids from a model folder (the model comes from config.json's name) equal
+    the plain model's, and the random-weights mode runs from a config.json alone, with the layers' statistics."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli = os.path.join(root, "bin", "gguf-infer")
+    model = models("B")
+    prompts = [random_tokens(n, model.cfg["vocab"], 70 + n) for n in (9, 1)]
+    args = [sys.executable, cli, "--model", model.folder, "--temperature", "0", "--repetition-penalty", "1", "--max-tokens", "6",
+            "--dtype", "float32", "--max-seq-len", "256", "--stop-ids", ""]
+    for p in prompts:
+        args += ["--prompt", ",".join(str(t) for t in p)]
+    p = subprocess.run(args, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    assert [[int(t) for t in l.split()] for l in lines] == [plain_lulisun.greedy(model.cfg, model.weights, q, 6) for q in prompts]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(lulisun_models.CONFIGS["A"]))
+    p = subprocess.run([sys.executable, cli, "--random-config", str(cfg_file), "--weights-seed", "3", "--random-prompts", "2:4:20",
+                        "-n", "5", "--max-seq-len", "128", "--dump-layer-stats"], capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len([l for l in p.stdout.splitlines() if l.strip()]) == 2 and "[L3]" in p.stderr + p.stdout
