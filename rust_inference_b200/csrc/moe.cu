@@ -64,7 +64,7 @@ template <> __device__ __forceinline__ void load4_f32<__nv_bfloat16>(const __nv_
 // the shared expert's gate row): a row is read once and multiplied with every token of the block, four
 // values at a time with as many independent sums as tokens.  Then warp k makes token k's choice.
 // Shared memory per token: score[E], choice[E], group score[G].
-template <typename T, bool VEC>
+template <typename T, bool VEC, int TOK>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* x, const float* __restrict__ router, const float* __restrict__ correction,
                  const float* __restrict__ gate_w, int* __restrict__ ids, float* __restrict__ weights,
@@ -80,16 +80,16 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
 
     for (int e = warp; e < experts + (gate_w != nullptr ? 1 : 0); e += ROUTE_WARPS) {
         const float* w = e < experts ? router + (size_t)e * width : gate_w;
-        float acc[ROUTE_TOKENS];
+        float acc[TOK];
 #pragma unroll
-        for (int k = 0; k < ROUTE_TOKENS; ++k) acc[k] = 0.f;
+        for (int k = 0; k < TOK; ++k) acc[k] = 0.f;
         if (VEC) {
-#pragma unroll 4
+#pragma unroll (TOK == 1 ? 8 : 4)
             for (int d = lane * 4; d < width; d += 128) {
                 const float4 w4 = *reinterpret_cast<const float4*>(w + d);
 #pragma unroll
-                for (int k = 0; k < ROUTE_TOKENS; ++k)
-                    if (k < n_here) {
+                for (int k = 0; k < TOK; ++k)
+                    if (TOK == 1 || k < n_here) {
                         float xv[4];
                         load4_f32<T>(x + (size_t)(tok0 + k) * width + d, xv);
                         acc[k] = fmaf(xv[0], w4.x, fmaf(xv[1], w4.y, fmaf(xv[2], w4.z, fmaf(xv[3], w4.w, acc[k]))));
@@ -99,12 +99,12 @@ moe_route_kernel(const T* x, const float* __restrict__ router, const float* __re
             for (int d = lane; d < width; d += 32) {
                 const float wv = w[d];
 #pragma unroll
-                for (int k = 0; k < ROUTE_TOKENS; ++k)
-                    if (k < n_here) acc[k] = fmaf(to_f32<T>(x[(size_t)(tok0 + k) * width + d]), wv, acc[k]);
+                for (int k = 0; k < TOK; ++k)
+                    if (TOK == 1 || k < n_here) acc[k] = fmaf(to_f32<T>(x[(size_t)(tok0 + k) * width + d]), wv, acc[k]);
             }
         }
 #pragma unroll
-        for (int k = 0; k < ROUTE_TOKENS; ++k) {
+        for (int k = 0; k < TOK; ++k) {
             if (k >= n_here) break;
             const float a = warp_sum(acc[k]);
             if (lane == 0) {
@@ -362,12 +362,14 @@ RI_API int ri_moe_route(const void* x, int dtype, const float* router, const flo
     const bool vec = width % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)router % 16 == 0 &&
                      (gate_w == nullptr || (uintptr_t)gate_w % 16 == 0);
     cudaError_t e;
-#define RI_ROUTE(T, V) launch_dependent(moe_route_kernel<T, V>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)x, router, \
-                                        correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top, groups, keep, \
-                                        per_block)
+#define RI_ROUTE_N(T, V, N) launch_dependent(moe_route_kernel<T, V, N>, blocks, ROUTE_WARPS * 32, smem, stream, (const T*)x, \
+                                             router, correction, gate_w, ids, weights, gate_out, n_tokens, width, experts, top,   \
+                                             groups, keep, per_block)
+#define RI_ROUTE(T, V) (per_block == 1 ? RI_ROUTE_N(T, V, 1) : per_block == 2 ? RI_ROUTE_N(T, V, 2) : RI_ROUTE_N(T, V, ROUTE_TOKENS))
     if (dtype == RI_F32) e = vec ? RI_ROUTE(float, true) : RI_ROUTE(float, false);
     else if (dtype == RI_BF16) e = vec ? RI_ROUTE(__nv_bfloat16, true) : RI_ROUTE(__nv_bfloat16, false);
     else return fail("moe_route: unknown dtype %d", dtype);
+#undef RI_ROUTE_N
 #undef RI_ROUTE
     return check_launch(e, "moe_route");
 }
