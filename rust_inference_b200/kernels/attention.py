@@ -5,6 +5,11 @@
                                  kernel (`attention_tcgen05`), with the mma.sync one behind it
   anything else                  the generic kernel (`attention_generic`): any head size, any
                                  dtype, float32 arithmetic
+
+Besides causality a mixer may limit a query's keys to the last `window` keys or to the query's own
+chunk of positions.  The tensor-core kernels take either as one signed span (`csrc/common.cuh:
+first_visible_key`); both at once, or values of another head size than the keys', go to the
+generic kernel.
 """
 from __future__ import annotations
 
