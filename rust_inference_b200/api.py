@@ -49,7 +49,8 @@ class Model:
         for entry in eng.model.cache_requests():
             for req in (entry if isinstance(entry, tuple) else (entry,)):
                 if req is not None and hasattr(req, "n_kv_heads"):
-                    per_position += req.n_kv_heads * (req.head_dim + (req.v_head_dim or req.head_dim)) * item
+                    values = 0 if getattr(req, "values_in_keys", False) else (req.v_head_dim or req.head_dim)
+                    per_position += req.n_kv_heads * (req.head_dim + values) * item
         return {"weight_bytes": eng.model.weight_bytes(), "weight_bytes_per_step": eng.model.weight_bytes(False),
                 "cache_bytes": eng.cache.bytes(), "cache_bytes_per_position": per_position}
 

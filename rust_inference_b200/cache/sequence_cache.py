@@ -8,7 +8,10 @@ form a *group* with storage of its own:
                dtype (V with a head size of its own when the request gives one).  A (page,
                kv head) is a dense [page_size, head_dim] tile.  Groups are keyed by (kv
                heads, head_dim, window, value head size), so layers that keep all keys and
-               layers that look at a window do not share storage.
+               layers that look at a window do not share storage.  A request may say that its
+               values are the leading channels of its keys (one row per position that serves as
+               both, as attention over a shared latent keeps it): then there is no V, and the
+               layer's `v` is its `k`.
   state group  [layers in group, slots, *shape]: state of fixed size per sequence, zeroed
                when the slot is handed out (a recurrent mixer's matrix state, for one).
 
@@ -38,6 +41,7 @@ class KVRequest:
     head_dim: int
     window: int | None = None      # None: the layer reads all keys
     v_head_dim: int | None = None  # None: values have the keys' head size
+    values_in_keys: bool = False   # the values are the first v_head_dim channels of the keys: no storage of their own
 
 
 @dataclass(frozen=True)
@@ -114,8 +118,14 @@ class SequenceCache:
             if isinstance(req, KVRequest):
                 shape = (len(users), n_pages, req.n_kv_heads, page_size, req.head_dim)
                 k = torch.zeros(shape, dtype=dtype, device=self.device)
-                v = torch.zeros(shape[:-1] + (req.v_head_dim or req.head_dim,), dtype=dtype, device=self.device)
-                self.groups[req] = (k, v)
+                if req.values_in_keys:
+                    if (req.v_head_dim or req.head_dim) > req.head_dim:
+                        raise ValueError(f"cache: values of {req.v_head_dim} channels do not fit inside keys of {req.head_dim}")
+                    v = k
+                    self.groups[req] = (k,)
+                else:
+                    v = torch.zeros(shape[:-1] + (req.v_head_dim or req.head_dim,), dtype=dtype, device=self.device)
+                    self.groups[req] = (k, v)
                 for j, (i, m) in enumerate(users):
                     place(i, m, KVLayer(k[j], v[j], req))
             elif isinstance(req, StateRequest):

@@ -13,7 +13,11 @@
 // limits them to the query's own block of `chunk` positions, counted from position 0 of the
 // sequence (floor(p / chunk) * chunk .. p); the dense decoder passes 0 for both.  Values may
 // have another head size than keys (`v_hd`), and the result is multiplied by `out_scale`
-// before it is rounded to the output type.
+// before it is rounded to the output type.  A value row need not be dense: `v_ld` is the distance
+// between the value rows of consecutive keys (v_hd when they have a cache of their own; the key head
+// size when the values are the leading channels of the keys, vcache == kcache).  The result of token t
+// and head h goes to out + t * out_ld + h * out_hs (out_hs = v_hd: heads side by side in a token's row;
+// out_hs = n_tokens * v_hd with out_ld = v_hd: head-major, a head's tokens consecutive).
 #include "common.cuh"
 
 using namespace ri;
@@ -30,7 +34,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
                     const int* __restrict__ token_pos, const int* __restrict__ token_seq,
                     const int* __restrict__ seq_slot, T* __restrict__ out, int out_ld, int n_heads,
                     int n_kv_heads, int hd, int v_hd, int page_size, float scale, int window, int chunk,
-                    float out_scale) {
+                    float out_scale, int v_ld, long long out_hs) {
     extern __shared__ float smem[];
     float* qs = smem;                 // [hd]
     float* ps = smem + hd;            // [THREADS]
@@ -83,7 +87,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
             if (d < v_hd) {
                 float o = acc[a] * alpha;
                 for (int jj = 0; jj < cn; ++jj)
-                    o = fmaf(ps[jj], to_f32<T>(vcache[(size_t)key_off[jj] * v_hd + d]), o);
+                    o = fmaf(ps[jj], to_f32<T>(vcache[(size_t)key_off[jj] * v_ld + d]), o);
                 acc[a] = o;
             }
         }
@@ -92,7 +96,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_ld, const T* __restrict__ kca
 #pragma unroll
     for (int a = 0; a < MAX_ACC; ++a) {
         const int d = tid + a * THREADS;
-        if (d < v_hd) out[(size_t)t * out_ld + h * v_hd + d] = from_f32<T>(acc[a] * inv);
+        if (d < v_hd) out[(size_t)t * out_ld + (size_t)h * out_hs + d] = from_f32<T>(acc[a] * inv);
     }
 }
 
@@ -103,11 +107,14 @@ RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, con
                                 const int* token_seq, const int* seq_slot, void* out, int out_ld, int dtype,
                                 int n_tokens, int n_heads, int n_kv_heads, int hd, int v_hd, int page_size,
                                 long long cache_rows, float scale, int window, int chunk, float out_scale,
-                                cudaStream_t stream) {
+                                int v_ld, long long out_hs, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads)
         return fail("attention: %d heads are not a multiple of %d kv heads", n_heads, n_kv_heads);
     if (v_hd <= 0) v_hd = hd;
+    if (v_ld <= 0) v_ld = v_hd;
+    if (out_hs <= 0) out_hs = v_hd;
+    if (v_ld < v_hd) return fail("attention: value rows %d apart hold %d values", v_ld, v_hd);
     if (v_hd > THREADS * MAX_ACC) return fail("attention: value head size %d exceeds %d", v_hd, THREADS * MAX_ACC);
     if (hd <= 0 || window < 0 || chunk < 0) return fail("attention: head size %d, window %d, chunk %d", hd, window, chunk);
     if (cache_rows > 0x7fffffffLL) return fail("attention: cache of %lld rows exceeds 2^31", cache_rows);
@@ -117,12 +124,12 @@ RI_API int ri_attention_generic(const void* q, int q_ld, const void* kcache, con
     if (dtype == RI_F32)
         attn_generic_kernel<float><<<grid, THREADS, smem, stream>>>(
             (const float*)q, q_ld, (const float*)kcache, (const float*)vcache, page_table, max_pages, token_pos,
-            token_seq, seq_slot, (float*)out, out_ld, n_heads, n_kv_heads, hd, v_hd, page_size, scale, window, chunk, out_scale);
+            token_seq, seq_slot, (float*)out, out_ld, n_heads, n_kv_heads, hd, v_hd, page_size, scale, window, chunk, out_scale, v_ld, out_hs);
     else if (dtype == RI_BF16)
         attn_generic_kernel<__nv_bfloat16><<<grid, THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_ld, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, page_table,
             max_pages, token_pos, token_seq, seq_slot, (__nv_bfloat16*)out, out_ld, n_heads, n_kv_heads, hd,
-            v_hd, page_size, scale, window, chunk, out_scale);
+            v_hd, page_size, scale, window, chunk, out_scale, v_ld, out_hs);
     else
         return fail("attention: unknown dtype %d", dtype);
     return check_launch("attention_generic");

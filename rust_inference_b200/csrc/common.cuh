@@ -100,6 +100,19 @@ __host__ __device__ __forceinline__ int first_visible_key(int pos, int span) {
     return 0;
 }
 
+// The form of a gated feed-forward's activation, for the contractions' gated epilogue:
+//   act(g, u) = g' * sigmoid(alpha * g') * (u' + shift),   g' = min(g, limit),  u' = clamp(u, -limit, limit).
+// Three floats in device memory {alpha, limit, shift}; a null pointer stands for SiLU(g) * u (alpha 1, no limit,
+// shift 0), which the formulas below reproduce exactly with those values.
+struct GateForm { float alpha, limit, shift; };
+__device__ __forceinline__ GateForm load_gate_form(const float* p) {
+    GateForm f;
+    f.alpha = p != nullptr ? p[0] : 1.f;
+    f.limit = p != nullptr ? p[1] : INFINITY;
+    f.shift = p != nullptr ? p[2] : 0.f;
+    return f;
+}
+
 // The reference's SiLU, stable on both sides (math.rs:137-146).
 __device__ __forceinline__ float silu_f32(float x) {
     if (x >= 0.f) {
@@ -108,6 +121,16 @@ __device__ __forceinline__ float silu_f32(float x) {
         float e = expf(x);
         return x * e / (1.f + e);
     }
+}
+
+// The gated activation with accurate exponentials (the 32-bit path); alpha 1 without limit and shift is silu_f32(g) * u.
+__device__ __forceinline__ float gated_f32(float g, float u, const GateForm& f) {
+    g = fminf(g, f.limit);
+    u = fmaxf(fminf(u, f.limit), -f.limit) + f.shift;
+    if (f.alpha == 1.f) return silu_f32(g) * u;
+    const float z = f.alpha * g;
+    const float sig = z >= 0.f ? 1.f / (1.f + expf(-z)) : expf(z) / (1.f + expf(z));
+    return g * sig * u;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -273,6 +296,7 @@ __device__ __forceinline__ bool in_range(long long i, long long limit, int check
 }
 }  // namespace ri
 #define RI_IN_LIMIT(i, which, check) ri::in_range((long long)(i), (long long)ri::g_limits[which], check, true)
+#define RI_IN_RANGE(i, limit, check) ri::in_range((long long)(i), (long long)(limit), check, true)
 #define RI_BLOCK_IN_RANGE(i, limit, check) ri::in_range((long long)(i), (long long)(limit), check, threadIdx.x == 0)
 #define RI_BLOCK_IN_LIMIT(i, which, check) \
     ri::in_range((long long)(i), (long long)ri::g_limits[which], check, threadIdx.x == 0)
@@ -291,6 +315,7 @@ __device__ __forceinline__ bool in_range(long long i, long long limit, int check
     }
 #else
 #define RI_IN_LIMIT(i, which, check) true
+#define RI_IN_RANGE(i, limit, check) true
 #define RI_BLOCK_IN_RANGE(i, limit, check) true
 #define RI_BLOCK_IN_LIMIT(i, which, check) true
 #define RI_DEFINE_BOUNDS()                                                                                     \

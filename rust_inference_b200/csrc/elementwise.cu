@@ -8,11 +8,11 @@
 using namespace ri;
 
 // ----------------------------------------------------------------------------
-// embedding: out[t, :] = table[ids[t], :]        (transformer.rs:74-75)
+// embedding: out[t, :] = table[ids[t], :] * scale        (transformer.rs:74-75; the factor is 1 there)
 // ----------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int hidden) {
+                                    float* __restrict__ out, int hidden, float scale) {
     const int t = blockIdx.x;
     let_next_kernel_start();
     wait_for_previous_kernels();          // the ids may come from the previous step's sampler
@@ -43,24 +43,24 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
                 if (i < n8) {
                     const T* e = reinterpret_cast<const T*>(&v[j]);
                     float4* dst = reinterpret_cast<float4*>(o + 8 * (size_t)i);
-                    dst[0] = make_float4(to_f32<T>(e[0]), to_f32<T>(e[1]), to_f32<T>(e[2]), to_f32<T>(e[3]));
-                    dst[1] = make_float4(to_f32<T>(e[4]), to_f32<T>(e[5]), to_f32<T>(e[6]), to_f32<T>(e[7]));
+                    dst[0] = make_float4(to_f32<T>(e[0]) * scale, to_f32<T>(e[1]) * scale, to_f32<T>(e[2]) * scale, to_f32<T>(e[3]) * scale);
+                    dst[1] = make_float4(to_f32<T>(e[4]) * scale, to_f32<T>(e[5]) * scale, to_f32<T>(e[6]) * scale, to_f32<T>(e[7]) * scale);
                 }
             }
         }
         return;
     }
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<T>(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
 }
 
 RI_API int ri_embed_gather(const void* table, int dtype, const int* ids, float* out, int n_tokens,
-                           int hidden, cudaStream_t stream) {
+                           int hidden, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     cudaError_t e = cudaSuccess;
     if (dtype == RI_F32)
-        e = launch_dependent(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (const float*)table, ids, out, hidden);
+        e = launch_dependent(embed_gather_kernel<float>, n_tokens, 256, 0, stream, (const float*)table, ids, out, hidden, scale);
     else if (dtype == RI_BF16)
-        e = launch_dependent(embed_gather_kernel<__nv_bfloat16>, n_tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden);
+        e = launch_dependent(embed_gather_kernel<__nv_bfloat16>, n_tokens, 256, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, scale);
     else
         return fail("embed_gather: unknown dtype %d", dtype);
     return check_launch(e, "embed_gather");
@@ -275,6 +275,160 @@ RI_API int ri_rmsnorm_pair(const float* x, const float* w_a, const float* w_b, v
     else
         return fail("rmsnorm_pair: unknown dtype %d", out_dtype);
     return check_launch(e, "rmsnorm_pair");
+}
+
+// ----------------------------------------------------------------------------
+// Layer norm with a weight and no bias: y = (x - mean) / sqrt(var + eps) * w, var the mean of the squared
+// deviations from the mean (taken in a second pass over the row, which stays in registers: no
+// E[x^2] - mean^2 cancellation).  Statistics in float32.  `rows` (may be null) picks the input rows.
+// ----------------------------------------------------------------------------
+namespace {
+// few rows: a block per row, PER float4s of the row per thread
+template <typename T, int PER>
+__global__ void __launch_bounds__(1024)
+layernorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                     T* __restrict__ out, int n, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x, n4 = n >> 2;
+    float4 wv[PER], xv[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        wv[j] = i < n4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const int in_row = rows ? rows[r] : r;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)in_row * n);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        xv[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (xv[j].x + xv[j].y) + (xv[j].z + xv[j].w);
+    }
+    const float mean = block_sum(sum, scratch) / (float)n;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n4) {
+            xv[j].x -= mean; xv[j].y -= mean; xv[j].z -= mean; xv[j].w -= mean;
+            ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+        }
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+    T* o = out + (size_t)r * n;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < n4)
+            store4<T>(o + 4 * i, xv[j].x * scale * wv[j].x, xv[j].y * scale * wv[j].y, xv[j].z * scale * wv[j].z,
+                      xv[j].w * scale * wv[j].w);
+    }
+}
+
+// many rows: a warp per row, CH float4s per lane, no block-wide barrier
+template <typename T, int CH>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                      T* __restrict__ out, int n_rows, int n, float eps) {
+    const int lane = threadIdx.x & 31, n4 = n >> 2;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    if (r >= n_rows) return;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * n);
+    float4 xv[CH];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int i = lane + j * 32;
+        xv[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (xv[j].x + xv[j].y) + (xv[j].z + xv[j].w);
+    }
+    const float mean = warp_sum(sum) / (float)n;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int i = lane + j * 32;
+        if (i < n4) {
+            xv[j].x -= mean; xv[j].y -= mean; xv[j].z -= mean; xv[j].w -= mean;
+            ss += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+        }
+    }
+    const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+    T* o = out + (size_t)r * n;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const int i = lane + j * 32;
+        if (i < n4) {
+            const float4 wv = reinterpret_cast<const float4*>(w)[i];
+            store4<T>(o + 4 * i, xv[j].x * scale * wv.x, xv[j].y * scale * wv.y, xv[j].z * scale * wv.z,
+                      xv[j].w * scale * wv.w);
+        }
+    }
+}
+
+// any width: a block per row, three passes over the row (it stays in L1)
+template <typename T>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const int* __restrict__ rows,
+                                 T* __restrict__ out, int n, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    let_next_kernel_start();
+    wait_for_previous_kernels();
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * n;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) sum += xr[i];
+    const float mean = block_sum(sum, scratch) / (float)n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float d = xr[i] - mean;
+        ss += d * d;
+    }
+    const float scale = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+    T* o = out + (size_t)r * n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>((xr[i] - mean) * scale * w[i]);
+}
+
+template <typename T>
+cudaError_t launch_layernorm(const float* x, const float* w, const int* rows, T* out, int n_rows, int n, float eps,
+                             cudaStream_t stream) {
+    const bool vec = n % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int n4 = n / 4;
+    if (vec && n_rows >= 256 && n4 <= 32 * 64) {
+        const int ch = (n4 + 31) / 32;
+        const int blocks = (n_rows + 7) / 8;
+        if (ch <= 8) return launch_dependent(layernorm_warp_kernel<T, 8>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+        if (ch <= 16) return launch_dependent(layernorm_warp_kernel<T, 16>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+        if (ch <= 32) return launch_dependent(layernorm_warp_kernel<T, 32>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+        return launch_dependent(layernorm_warp_kernel<T, 64>, blocks, 256, 0, stream, x, w, rows, out, n_rows, n, eps);
+    }
+    if (vec && n4 <= 4 * 1024) {
+        int threads = ((n4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        const int per = (n4 + threads - 1) / threads;
+        if (per <= 1) return launch_dependent(layernorm_vec_kernel<T, 1>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+        if (per <= 2) return launch_dependent(layernorm_vec_kernel<T, 2>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+        return launch_dependent(layernorm_vec_kernel<T, 4>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+    }
+    const int threads = n >= 1024 ? 256 : 128;
+    return launch_dependent(layernorm_kernel<T>, n_rows, threads, 0, stream, x, w, rows, out, n, eps);
+}
+}  // namespace
+
+RI_API int ri_layernorm(const float* x, const float* w, const int* rows, void* out, int out_dtype,
+                        int n_rows, int n, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    cudaError_t e = cudaSuccess;
+    if (out_dtype == RI_F32)
+        e = launch_layernorm<float>(x, w, rows, (float*)out, n_rows, n, eps, stream);
+    else if (out_dtype == RI_BF16)
+        e = launch_layernorm<__nv_bfloat16>(x, w, rows, (__nv_bfloat16*)out, n_rows, n, eps, stream);
+    else
+        return fail("layernorm: unknown dtype %d", out_dtype);
+    return check_launch(e, "layernorm");
 }
 
 // ----------------------------------------------------------------------------
@@ -495,6 +649,119 @@ RI_API int ri_rope_cache_write(void* qkv, int dtype, int ld, const float* cos_t,
     else
         return fail("rope_cache_write: unknown dtype %d", dtype);
     return check_launch(e, "rope_cache_write");
+}
+
+// ----------------------------------------------------------------------------
+// Rotary position encoding + cache write for heads that are normalised first.
+//
+// qkv is [n_tokens, ld] with q at column 0 (n_heads * hd) and k after it (n_kv_heads * hd).  Every q and k
+// head is divided by its root mean square, sqrt(mean(x^2) + eps), and multiplied by a weight of hd values
+// that all heads share (q_w for queries, k_w for keys; null: the head is left as it is); then the first
+// `rot` channels are rotated as above.  q is rewritten in place, k goes to the cache.  The values are
+// either the columns after k (n_kv_heads * v_hd, copied), or, with `v_from_k`, the key heads as they were
+// projected, before norm and rotation (v_hd == hd; qkv then has no value columns).
+// A warp per (token, head): the head is read once into shared memory as float32.
+// ----------------------------------------------------------------------------
+namespace {
+constexpr int NORMED_ROPE_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(NORMED_ROPE_WARPS * 32)
+rope_normed_cache_write_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                               const float* __restrict__ sin_t, const float* __restrict__ q_w,
+                               const float* __restrict__ k_w, float eps, const int* __restrict__ token_pos,
+                               const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                               const int* __restrict__ page_table, int max_pages, T* __restrict__ kcache,
+                               T* __restrict__ vcache, int n_tokens, int n_heads, int n_kv_heads, int hd, int page_size,
+                               int style, int write_kv, int rot, int v_hd, int v_from_k) {
+    extern __shared__ float head_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* x = head_smem + (size_t)warp * hd;
+    const int heads = n_heads + n_kv_heads + (v_from_k ? 0 : n_kv_heads);     // copied value heads count as items too
+    const long long item = (long long)blockIdx.x * NORMED_ROPE_WARPS + warp;
+    let_next_kernel_start();
+    wait_for_previous_kernels();          // the projections come from the previous kernel
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads), h = (int)(item % heads);
+    if (h >= n_heads && !write_kv) return;
+    const int pos = token_pos[t];
+    const int half = rot >> 1;
+    const float* c = cos_t + (size_t)pos * half;
+    const float* s = sin_t + (size_t)pos * half;
+    T* row = qkv + (size_t)t * ld;
+
+    size_t cache_row = 0;                 // in rows of one kv head
+    if (h >= n_heads) {
+        const int slot = seq_slot[token_seq[t]];
+        if (!RI_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT) || !RI_IN_RANGE(pos / page_size, max_pages, RI_CHECK_PAGE_INDEX)) return;
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        if (!RI_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) return;
+        cache_row = (size_t)page * n_kv_heads * page_size + (pos % page_size);
+    }
+    if (h >= n_heads + n_kv_heads) {      // a value head of its own: copy
+        const int kh = h - n_heads - n_kv_heads;
+        const T* src = row + (size_t)(n_heads + n_kv_heads) * hd + (size_t)kh * v_hd;
+        T* dst = vcache + (cache_row + (size_t)kh * page_size) * v_hd;
+        for (int d = lane; d < v_hd; d += 32) dst[d] = src[d];
+        return;
+    }
+    const bool is_q = h < n_heads;
+    const int kh = h - n_heads;
+    T* src = row + (size_t)h * hd;        // q heads, then k heads: one run of columns
+    const float* w = is_q ? q_w : k_w;
+    T* vdst = (!is_q && v_from_k) ? vcache + (cache_row + (size_t)kh * page_size) * hd : nullptr;
+    float ss = 0.f;
+    for (int d = lane; d < hd; d += 32) {
+        const T raw = src[d];
+        if (vdst != nullptr) vdst[d] = raw;                       // the value: the key as projected
+        const float v = to_f32<T>(raw);
+        x[d] = v;
+        ss += v * v;
+    }
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        for (int d = lane; d < hd; d += 32) x[d] = x[d] * scale * w[d];
+    }
+    __syncwarp();
+    T* dst = is_q ? src : kcache + (cache_row + (size_t)kh * page_size) * hd;
+    for (int i = lane; i < half; i += 32) {
+        const int i0 = style == 0 ? i : 2 * i;
+        const int i1 = style == 0 ? i + half : 2 * i + 1;
+        const float x0 = x[i0], x1 = x[i1];
+        dst[i0] = from_f32<T>(x0 * c[i] - x1 * s[i]);
+        dst[i1] = from_f32<T>(x0 * s[i] + x1 * c[i]);
+    }
+    for (int d = rot + lane; d < hd; d += 32) dst[d] = from_f32<T>(x[d]);
+}
+}  // namespace
+
+RI_API int ri_rope_normed_cache_write(void* qkv, int dtype, int ld, const float* cos_t, const float* sin_t,
+                                      const float* q_w, const float* k_w, float eps, const int* token_pos,
+                                      const int* token_seq, const int* seq_slot, const int* page_table, int max_pages,
+                                      void* kcache, void* vcache, int n_tokens, int n_heads, int n_kv_heads, int hd,
+                                      int page_size, int style, int write_kv, int rot, int v_hd, int v_from_k,
+                                      cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (rot <= 0) rot = hd;
+    if (v_hd <= 0) v_hd = hd;
+    if (rot % 2 || rot > hd) return fail("rope_normed_cache_write: %d rotated channels of a head of %d", rot, hd);
+    if (style != 0 && style != 1) return fail("rope_normed_cache_write: unknown style %d", style);
+    if (v_from_k && v_hd != hd) return fail("rope_normed_cache_write: values taken from keys of %d have the size %d", hd, v_hd);
+    const size_t smem = (size_t)NORMED_ROPE_WARPS * hd * sizeof(float);
+    if (smem > 48 * 1024) return fail("rope_normed_cache_write: heads of %d exceed %d", hd, 48 * 1024 / 4 / NORMED_ROPE_WARPS);
+    const int heads = n_heads + n_kv_heads + (v_from_k ? 0 : n_kv_heads);
+    const long long items = (long long)n_tokens * heads;
+    const unsigned blocks = (unsigned)((items + NORMED_ROPE_WARPS - 1) / NORMED_ROPE_WARPS);
+    cudaError_t e;
+#define RI_NORMED_ROPE(T) launch_dependent(rope_normed_cache_write_kernel<T>, blocks, NORMED_ROPE_WARPS * 32, smem, stream, \
+        (T*)qkv, ld, cos_t, sin_t, q_w, k_w, eps, token_pos, token_seq, seq_slot, page_table, max_pages, (T*)kcache, \
+        (T*)vcache, n_tokens, n_heads, n_kv_heads, hd, page_size, style, write_kv, rot, v_hd, v_from_k)
+    if (dtype == RI_F32) e = RI_NORMED_ROPE(float);
+    else if (dtype == RI_BF16) e = RI_NORMED_ROPE(__nv_bfloat16);
+    else return fail("rope_normed_cache_write: unknown dtype %d", dtype);
+#undef RI_NORMED_ROPE
+    return check_launch(e, "rope_normed_cache_write");
 }
 
 // ----------------------------------------------------------------------------

@@ -10,7 +10,8 @@
 //   1  out<f32> = acc + bias                          (logits, transformer.rs:97)
 //   2  out<f32> += acc                                (o / down projection onto the residual
 //                                                      stream, transformer.rs:38-39, :47)
-//   3  out<T>   = silu(acc) * acc2, acc2 = X * W2^T   (SwiGLU, mlp.rs:35-43)
+//   3  out<T>   = silu(acc) * acc2, acc2 = X * W2^T   (SwiGLU, mlp.rs:35-43); `bias`, when not null, points to
+//                                                      the three constants of another gate form (`GateForm`)
 #include "common.cuh"
 
 using namespace ri;
@@ -64,6 +65,7 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __re
     const int lk = (tid & 3) * 4;       // 0,4,8,12: first k of its 4 elements
     const int ty = tid >> 4, tx = tid & 15;
 
+    const GateForm gf = load_gate_form(DUAL ? bias : nullptr);
     float acc[TM][TN];
     float acc2[DUAL ? TM : 1][DUAL ? TN : 1];
 #pragma unroll
@@ -126,7 +128,7 @@ gemm_simt_kernel(const T* __restrict__ X, const T* __restrict__ W, const T* __re
             } else if (MODE == 2) {
                 reinterpret_cast<float*>(out_)[o] += v;
             } else {
-                reinterpret_cast<T*>(out_)[o] = from_f32<T>(silu_f32(v) * acc2[i][j]);
+                reinterpret_cast<T*>(out_)[o] = from_f32<T>(gated_f32(v, acc2[i][j], gf));
             }
         }
     }

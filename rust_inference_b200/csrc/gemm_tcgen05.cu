@@ -28,7 +28,9 @@
 //   2  out<f32> += acc                                (o / down projection onto the residual
 //                                                      stream, transformer.rs:38-39, :47)
 //   3  out<bf16> = silu(acc) * acc2, acc2 = X W2^T    (SwiGLU, mlp.rs:35-43): two accumulators
-//                                                      fed by the same X tile
+//                                                      fed by the same X tile.  This epilogue takes no bias: its
+//                                                      `bias` argument, when not null, points to the three
+//                                                      constants of another gate form (`GateForm`, common.cuh)
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out stores a code in the
 // host-visible status word, the CTA stops issuing work, waits (bounded) for its own
@@ -63,9 +65,15 @@ __host__ __device__ constexpr uint32_t make_idesc(int tn) {
 // x e^x / (1 + e^x) (math.rs:137-146); the fast exponential and division are exact to a few ulp of
 // float32, far below bf16's 8 bits.
 __device__ __forceinline__ float silu_to_bf16(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+// The gated epilogue in its general form (`GateForm`), with the same fast exponential and division.
+__device__ __forceinline__ float gated_to_bf16(float g, float u, const GateForm& f) {
+    g = fminf(g, f.limit);
+    u = fmaxf(fminf(u, f.limit), -f.limit) + f.shift;
+    return __fdividef(g, 1.f + __expf(-f.alpha * g)) * u;
+}
 
 template <int MODE>
-__device__ __forceinline__ void store_result(void* out_, size_t o, float acc, float bias, float acc2) {
+__device__ __forceinline__ void store_result(void* out_, size_t o, float acc, float bias, float acc2, const GateForm& gf) {
     if (MODE == 0) {
         reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(acc + bias);
     } else if (MODE == 1) {
@@ -75,7 +83,7 @@ __device__ __forceinline__ void store_result(void* out_, size_t o, float acc, fl
         // waits on a load
         atomicAdd(reinterpret_cast<float*>(out_) + o, acc);
     } else {
-        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(silu_to_bf16(acc) * acc2);
+        reinterpret_cast<__nv_bfloat16*>(out_)[o] = __float2bfloat16_rn(gated_to_bf16(acc, acc2, gf));
     }
 }
 
@@ -278,7 +286,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!landed || abort_flag) break;
             const int f = f0 + lane_base + lane;
             const bool f_ok = f < n_feat;
-            const float b = (bias != nullptr && f_ok) ? bias[f] : 0.f;
+            const float b = (MODE != 3 && bias != nullptr && f_ok) ? bias[f] : 0.f;
+            const GateForm gf = load_gate_form(MODE == 3 ? bias : nullptr);
             const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * ACC_COLS);
 #pragma unroll 1
             for (int c0 = 0; c0 < tn; c0 += 16) {
@@ -296,12 +305,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             store_result<MODE>(out_, o0 + (size_t)j * n_feat, __uint_as_float(v[j]), b,
-                                               DUAL ? __uint_as_float(u[j]) : 0.f);
+                                               DUAL ? __uint_as_float(u[j]) : 0.f, gf);
                     } else {
                         for (int j = 0; j < 16; ++j)
                             if (t0 + c0 + j < n_tok)
                                 store_result<MODE>(out_, o0 + (size_t)j * n_feat, __uint_as_float(v[j]), b,
-                                                   DUAL ? __uint_as_float(u[j]) : 0.f);
+                                                   DUAL ? __uint_as_float(u[j]) : 0.f, gf);
                     }
                 }
             }
@@ -345,6 +354,7 @@ __device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, i
                                               const float* __restrict__ bias, void* __restrict__ out_,
                                               bool pieces = false) {     // MODE 2: other work items add to the same tile
     constexpr int FEATS = DUAL ? TM_ROWS / 2 : TM_ROWS;
+    const GateForm gf = load_gate_form(MODE == 3 ? bias : nullptr);     // the gated epilogue's constants come in `bias`
 #pragma unroll 1
     for (int c0 = 0; c0 < FEATS; c0 += 16) {
         if (f0 + c0 >= n_feat) break;                       // uniform over the warp
@@ -359,7 +369,7 @@ __device__ __forceinline__ void tm_write_tile(uint32_t trow, int t, bool t_ok, i
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float a = __uint_as_float(v[j]);
-            if (MODE == 3) r[j] = silu_to_bf16(a) * __uint_as_float(u[j]);
+            if (MODE == 3) r[j] = gated_to_bf16(a, __uint_as_float(u[j]), gf);
             else if (MODE == 2) r[j] = a;
             else r[j] = a + ((bias != nullptr && f0 + c0 + j < n_feat) ? bias[f0 + c0 + j] : 0.f);
         }

@@ -129,3 +129,13 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
         ctx.seq_slot, out, n_tokens=qkv.shape[0], n_heads=n_heads, n_kv_heads=n_kv_heads,
         head_dim=head_dim, page_size=ctx.page_size, scale=scale, window=window, chunk=chunk or 0,
         v_head_dim=v_head_dim, out_scale=out_scale)
+
+
+def latent_attention(q_wide, cache_layer, out, ctx, *, n_heads, key_dim, rank, scale):
+    """Attention of n_heads query heads over ONE kv head whose keys are the cached rows [key_dim] and whose
+    values are the rows' first `rank` channels (no storage of their own); causal.  q_wide is
+    [T, n_heads * key_dim]; out is head-major, [n_heads, T, rank]."""
+    return ops.attention_generic(
+        q_wide, q_wide.shape[1], cache_layer.k, cache_layer.k, ctx.page_table, ctx.token_pos, ctx.token_seq,
+        ctx.seq_slot, out, n_tokens=q_wide.shape[0], n_heads=n_heads, n_kv_heads=1, head_dim=key_dim,
+        page_size=ctx.page_size, scale=scale, v_head_dim=rank, values_in_keys=True, head_major=True)

@@ -33,6 +33,7 @@ MODULES = {
     "recurrent": "recurrent.cu",
     "moe": "moe.cu",
     "moe_tcgen05": "moe_tcgen05.cu",
+    "latent": "latent.cu",
     "wait_probe": "wait_probe.cu",
     "host_runtime": "host_runtime.cpp",
 }

@@ -55,12 +55,13 @@ def into_residual(x, w: Weight, residual, ctx):
     return ops.gemm_simt(x, w.t, residual, ops.EPI_RESIDUAL)
 
 
-def gated(x, w_gate: Weight, w_up: Weight, out, ctx):
-    """out<run dtype> = silu(x Wg^T) * (x Wu^T)."""
+def gated(x, w_gate: Weight, w_up: Weight, out, ctx, form=None):
+    """out<run dtype> = silu(x Wg^T) * (x Wu^T); with `form` (float32 [3] on the device: alpha, limit, shift)
+    out = g' sigmoid(alpha g') (u' + shift), g' = min(x Wg^T, limit), u' = clamp(x Wu^T, -limit, limit)."""
     if _use_tensor_cores(x, w_gate):
         from . import tcgen05
-        return tcgen05.gemm(x, w_gate, out, ops.EPI_SILU_MUL, ctx, w2=w_up)
-    return ops.gemm_simt(x, w_gate.t, out, ops.EPI_SILU_MUL, w2=w_up.t)
+        return tcgen05.gemm(x, w_gate, out, ops.EPI_SILU_MUL, ctx, w2=w_up, gate_form=form)
+    return ops.gemm_simt(x, w_gate.t, out, ops.EPI_SILU_MUL, w2=w_up.t, gate_form=form)
 
 
 def accumulate_split(x, w: Weight, acc, ctx) -> bool:

@@ -161,15 +161,15 @@ def timeline_read(strict: bool = True) -> list:
 
 
 # ----------------------------------------------------------------------------
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, :] = table[ids[t], :] widened to float32.  ids: int32 [T]; out: float32 [T, H]."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t, :] = table[ids[t], :] * scale, widened to float32 first.  ids: int32 [T]; out: float32 [T, H]."""
     _need_cuda(table, ids, out)
     n, hidden = out.shape
     _need(ids.dtype == torch.int32 and ids.numel() == n, "embed_gather: ids must be int32 [T]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
           and table.shape[1] == hidden, "embed_gather: bad out/table")
     _call("elementwise", "ri_embed_gather", _p(table), c_int(dtype_code(table.dtype)), _p(ids), _p(out),
-          c_int(n), c_int(hidden), _stream())
+          c_int(n), c_int(hidden), c_float(scale), _stream())
     return out
 
 
@@ -203,6 +203,58 @@ def rmsnorm_pair(x: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor
           "rmsnorm_pair: two outputs of one shape and dtype")
     _call("elementwise", "ri_rmsnorm_pair", _p(x), _p(weight_a), _p(weight_b), _p(out_a), _p(out_b),
           c_int(dtype_code(out_a.dtype)), c_int(n_rows), c_int(n), c_float(eps), _stream())
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, :] = (x - mean) / sqrt(var + eps) * weight of the row x[rows[r] or r, :] (no bias; var: the mean of
+    the squared deviations).  x, weight float32; out float32 or bfloat16."""
+    _need_cuda(x, weight, out, rows)
+    n_rows, n = out.shape
+    _need(x.dtype == torch.float32 and weight.dtype == torch.float32, "layernorm: x and weight must be float32")
+    _need(x.is_contiguous() and out.is_contiguous() and x.shape[-1] == n and weight.numel() == n,
+          "layernorm: bad shapes")
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.numel() == n_rows, "layernorm: rows must be int32 [R]")
+    else:
+        _need(x.shape[0] >= n_rows, "layernorm: x has fewer rows than out")
+    _call("elementwise", "ri_layernorm", _p(x), _p(weight), _p(rows), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n_rows), c_int(n), c_float(eps), _stream())
+    return out
+
+
+def rope_normed_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, q_weight, k_weight, eps: float,
+                            token_pos, token_seq, seq_slot, page_table: torch.Tensor, kcache, vcache, *, n_heads: int,
+                            n_kv_heads: int, head_dim: int, page_size: int, style: int, write_kv: bool,
+                            rot_dims: int | None = None, v_head_dim: int | None = None, values_from_keys: bool = False) -> None:
+    """`rope_cache_write` for heads that are RMS-normalised before they are rotated: every q head times
+    q_weight / rms (float32 [head_dim], shared by the heads; None: not normalised), every k head likewise
+    with k_weight.  With values_from_keys qkv holds no values: the cache's values are the key heads as
+    projected, before norm and rotation."""
+    _need_cuda(qkv, cos, sin, q_weight, k_weight, token_pos, token_seq, seq_slot, page_table, kcache, vcache)
+    n = qkv.shape[0]
+    rot = head_dim if rot_dims is None else int(rot_dims)
+    v_hd = head_dim if v_head_dim is None else int(v_head_dim)
+    cols = (n_heads + n_kv_heads) * head_dim + (0 if values_from_keys else n_kv_heads * v_hd)
+    _need(qkv.is_contiguous() and qkv.shape[1] >= cols, "rope_normed_cache_write: qkv holds too few columns")
+    _need(0 < rot <= head_dim and rot % 2 == 0, "rope_normed_cache_write: rotated channels must be even and at most head_dim")
+    _need(not values_from_keys or v_hd == head_dim, "rope_normed_cache_write: values taken from the keys have their size")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot // 2
+          and cos.is_contiguous() and sin.is_contiguous(),
+          "rope_normed_cache_write: tables must be float32 [positions, rotated channels / 2]")
+    for w in (q_weight, k_weight):
+        _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == head_dim),
+              "rope_normed_cache_write: norm weights must be float32 [head_dim]")
+    if write_kv:
+        _need(kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous()
+              and vcache.is_contiguous(), "rope_normed_cache_write: cache dtype/layout")
+        _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim)
+              and tuple(vcache.shape[1:]) == (n_kv_heads, page_size, v_hd), "rope_normed_cache_write: cache shape")
+    _call("elementwise", "ri_rope_normed_cache_write", _p(qkv), c_int(dtype_code(qkv.dtype)), c_int(qkv.shape[1]),
+          _p(cos), _p(sin), _p(q_weight), _p(k_weight), c_float(eps), _p(token_pos), _p(token_seq), _p(seq_slot),
+          _p(page_table), c_int(page_table.shape[1]), _p(kcache), _p(vcache), c_int(n), c_int(n_heads), c_int(n_kv_heads),
+          c_int(head_dim), c_int(page_size), c_int(style), c_int(1 if write_kv else 0), c_int(rot), c_int(v_hd),
+          c_int(1 if values_from_keys else 0), _stream())
 
 
 def rope_cache_write(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, token_pos, token_seq,
@@ -271,8 +323,11 @@ EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SILU_MUL = 0, 1, 2, 3
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
-              bias: torch.Tensor | None = None, w2: torch.Tensor | None = None) -> torch.Tensor:
-    """out = x @ w.T with the chosen epilogue, on the FFMA pipe (float32 accumulate)."""
+              bias: torch.Tensor | None = None, w2: torch.Tensor | None = None,
+              gate_form: torch.Tensor | None = None) -> torch.Tensor:
+    """out = x @ w.T with the chosen epilogue, on the FFMA pipe (float32 accumulate).  gate_form (gated
+    epilogue only): float32 [3] on the device, {alpha, limit, shift} of g' sigmoid(alpha g') (u' + shift) with
+    g' = min(g, limit), u' = clamp(u, -limit, limit); None: SiLU(g) * u."""
     _need_cuda(x, w, out, bias, w2)
     m, k = x.shape
     n = w.shape[0]
@@ -284,6 +339,10 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
         _need(bias.dtype == torch.float32 and bias.numel() == n, "gemm: bias must be float32 [N]")
     if w2 is not None:
         _need(w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous(), "gemm: second matrix")
+    if gate_form is not None:
+        _need(mode == EPI_SILU_MUL and bias is None and gate_form.is_cuda and gate_form.dtype == torch.float32
+              and gate_form.numel() == 3, "gemm: a gate form is three float32 constants of the gated epilogue")
+        bias = gate_form                      # the gated epilogue takes no bias: its constants travel in that argument
     _call("gemm_simt", "ri_gemm_simt", _p(x), _p(w), _p(w2), _p(bias), _p(out), c_int(dtype_code(x.dtype)),
           c_int(mode), c_int(m), c_int(n), c_int(k), _stream())
     return out
@@ -292,23 +351,32 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, *,
 def attention_generic(q: torch.Tensor, q_ld: int, kcache, vcache, page_table, token_pos, token_seq,
                       seq_slot, out: torch.Tensor, *, n_tokens: int, n_heads: int, n_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: int = 0, chunk: int = 0,
-                      v_head_dim: int | None = None, out_scale: float = 1.0) -> torch.Tensor:
+                      v_head_dim: int | None = None, out_scale: float = 1.0, values_in_keys: bool = False,
+                      head_major: bool = False) -> torch.Tensor:
     """Attention of every given token over its slot's cached keys 0..position (any sizes), limited to
     the last `window` keys and / or to the query's own block of `chunk` positions when those are not 0;
-    values of head size v_head_dim (default: head_dim); the result times out_scale."""
+    values of head size v_head_dim (default: head_dim); the result times out_scale.  values_in_keys: the
+    values are the first v_head_dim channels of the keys (vcache is not read).  head_major: out is
+    [heads, tokens, v_head_dim] instead of [tokens, heads * v_head_dim]."""
     _need_cuda(q, kcache, vcache, page_table, token_pos, token_seq, seq_slot, out)
-    _need(q.dtype == kcache.dtype == vcache.dtype == out.dtype, "attention: dtypes differ")
     v_hd = head_dim if v_head_dim is None else int(v_head_dim)
-    _need(out.is_contiguous() and out.shape == (n_tokens, n_heads * v_hd), "attention: out shape")
+    if values_in_keys:
+        _need(v_hd <= head_dim, "attention: values inside keys cannot be wider than the keys")
+        vcache = kcache
+    _need(q.dtype == kcache.dtype == vcache.dtype == out.dtype, "attention: dtypes differ")
+    _need(out.is_contiguous() and out.numel() == n_tokens * n_heads * v_hd, "attention: out shape")
     _need(tuple(kcache.shape[1:]) == (n_kv_heads, page_size, head_dim)
-          and tuple(vcache.shape[1:]) == (n_kv_heads, page_size, v_hd) and kcache.shape[0] == vcache.shape[0],
-          "attention: cache shape")
+          and (values_in_keys or tuple(vcache.shape[1:]) == (n_kv_heads, page_size, v_hd))
+          and kcache.shape[0] == vcache.shape[0], "attention: cache shape")
     rows = kcache.shape[0] * kcache.shape[1] * kcache.shape[2]
+    out_ld = v_hd if head_major else n_heads * v_hd
+    out_hs = n_tokens * v_hd if head_major else v_hd
     _call("attention_generic", "ri_attention_generic", _p(q), c_int(q_ld), _p(kcache), _p(vcache),
           _p(page_table), c_int(page_table.shape[1]), _p(token_pos), _p(token_seq), _p(seq_slot), _p(out),
-          c_int(out.shape[1]), c_int(dtype_code(q.dtype)), c_int(n_tokens), c_int(n_heads),
+          c_int(out_ld), c_int(dtype_code(q.dtype)), c_int(n_tokens), c_int(n_heads),
           c_int(n_kv_heads), c_int(head_dim), c_int(v_hd), c_int(page_size), c_longlong(rows), c_float(scale),
-          c_int(window), c_int(chunk), c_float(out_scale), _stream())
+          c_int(window), c_int(chunk), c_float(out_scale), c_int(head_dim if values_in_keys else v_hd),
+          c_longlong(out_hs), _stream())
     return out
 
 
@@ -611,3 +679,64 @@ def moe_combine(residual: torch.Tensor, y: torch.Tensor, weights: torch.Tensor, 
           "moe_combine: the shared result and its gate go together")
     _call("moe", "ri_moe_combine", _p(residual), _p(y), _p(weights), _p(shared_y), _p(gate), _p(place), c_int(n),
           c_int(width), c_int(top), _stream())
+
+
+# ---- attention over a shared low-rank latent (csrc/latent.cu) ------------------------------------------
+def latent_prepare(proj: torch.Tensor, cos, sin, latent_weight, eps: float, token_pos, token_seq, seq_slot, page_table,
+                   cache, q_nope: torch.Tensor, q_wide: torch.Tensor, offsets, order, tiles, n_tiles, *, n_heads: int,
+                   head_dim: int, rot_dim: int, rank: int, rot_dims: int, style: int, page_size: int, write_kv: bool,
+                   tile_rows: int) -> None:
+    """From the projection [T, heads * (head_dim + rot_dim) (+ rank + rot_dim ...)]: the heads' unrotated query
+    parts head by head into q_nope [heads, T, head_dim], their rotated parts into the last rot_dim channels of
+    q_wide [T, heads, rank + rot_dim]; with write_kv the RMS-normalised latent (times latent_weight) and the rotated
+    key part into the token's row of `cache` [pages, 1, page_size, rank + rot_dim]; and the lists of the per-head
+    grouped products (head h owns rows h * T .. (h + 1) * T, in tiles of tile_rows)."""
+    _need_cuda(proj, cos, sin, latent_weight, token_pos, token_seq, seq_slot, page_table, cache, q_nope, q_wide,
+               offsets, order, tiles, n_tiles)
+    n = proj.shape[0]
+    wide = rank + rot_dim
+    need_cols = n_heads * (head_dim + rot_dim) + (wide if write_kv else 0)
+    _need(proj.is_contiguous() and proj.shape[1] >= need_cols, "latent_prepare: the projection holds too few columns")
+    _need(q_nope.dtype == proj.dtype and q_wide.dtype == proj.dtype and q_nope.is_contiguous() and q_wide.is_contiguous()
+          and q_nope.numel() == n * n_heads * head_dim and q_wide.numel() == n * n_heads * wide, "latent_prepare: query buffers")
+    _need(cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rot_dims // 2 and cos.is_contiguous()
+          and sin.is_contiguous() and 0 < rot_dims <= rot_dim and rot_dims % 2 == 0, "latent_prepare: rotation tables")
+    if write_kv:
+        _need(latent_weight is not None and latent_weight.dtype == torch.float32 and latent_weight.numel() == rank,
+              "latent_prepare: the latent's norm weight must be float32 [rank]")
+        _need(cache.dtype == proj.dtype and cache.is_contiguous() and tuple(cache.shape[1:]) == (1, page_size, wide),
+              "latent_prepare: cache shape")
+    per_head = -(-n // tile_rows)
+    for t in (offsets, order, tiles, n_tiles):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), "latent_prepare: int32 lists")
+    _need(offsets.numel() >= n_heads + 1 and order.numel() >= n_heads * n and tiles.numel() >= 2 * n_heads * per_head,
+          "latent_prepare: lists too small")
+    _call("latent", "ri_latent_prepare", _p(proj), c_int(dtype_code(proj.dtype)), c_int(proj.shape[1]), _p(cos), _p(sin),
+          _p(latent_weight), c_float(eps), _p(token_pos), _p(token_seq), _p(seq_slot), _p(page_table),
+          c_int(page_table.shape[1]), _p(cache), _p(q_nope), _p(q_wide), _p(offsets), _p(order), _p(tiles), _p(n_tiles),
+          c_int(n), c_int(n_heads), c_int(head_dim), c_int(rot_dim), c_int(rank), c_int(rot_dims), c_int(style),
+          c_int(page_size), c_int(1 if write_kv else 0), c_int(tile_rows), _stream())
+
+
+def latent_widen(q_lat: torch.Tensor, q_wide: torch.Tensor, *, n_tokens: int, n_heads: int, rank: int, rot_dim: int) -> None:
+    """q_wide[t, h, :rank] = q_lat[h, t, :] (float32 [heads, T, rank] into the run dtype's wide query rows)."""
+    _need_cuda(q_lat, q_wide)
+    _need(q_lat.dtype == torch.float32 and q_lat.is_contiguous() and q_lat.numel() == n_tokens * n_heads * rank
+          and q_wide.is_contiguous() and q_wide.numel() == n_tokens * n_heads * (rank + rot_dim), "latent_widen: shapes")
+    _call("latent", "ri_latent_widen", _p(q_lat), _p(q_wide), c_int(dtype_code(q_wide.dtype)), c_int(n_tokens),
+          c_int(n_heads), c_int(rank), c_int(rot_dim), _stream())
+
+
+def latent_gate(v: torch.Tensor, gates: torch.Tensor | None, out: torch.Tensor, *, n_tokens: int, n_heads: int,
+                v_head_dim: int) -> None:
+    """out[t, h * v_head_dim + j] = v[h, t, j] * sigmoid(gates[t, h]) (v float32, head by head; gates a view of
+    columns of the projection, row stride gates.stride(0); None: no gate)."""
+    _need_cuda(v, gates, out)
+    _need(v.dtype == torch.float32 and v.is_contiguous() and v.numel() == n_tokens * n_heads * v_head_dim
+          and out.is_contiguous() and out.shape == (n_tokens, n_heads * v_head_dim), "latent_gate: shapes")
+    ld = 0
+    if gates is not None:
+        _need(gates.dtype == out.dtype and gates.shape == (n_tokens, n_heads) and gates.stride(1) == 1, "latent_gate: gates")
+        ld = gates.stride(0)
+    _call("latent", "ri_latent_gate", _p(v), _p(gates), c_int(ld), _p(out), c_int(dtype_code(out.dtype)), c_int(n_tokens),
+          c_int(n_heads), c_int(v_head_dim), _stream())

@@ -116,7 +116,8 @@ def _x_map(x: torch.Tensor, tn: int) -> torch.Tensor:
     return m
 
 
-def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, w2=None, split_k: int | None = None):
+def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, w2=None, split_k: int | None = None,
+         gate_form=None):
     _need_cuda(x, w.t, out, bias)
     m, k = x.shape
     n = w.n
@@ -130,6 +131,11 @@ def gemm(x: torch.Tensor, w, out: torch.Tensor, mode: int, ctx=None, bias=None, 
     if w2 is not None:
         _need((w2.n, w2.k) == (n, k) and w2.t.dtype == torch.bfloat16, "gemm_tcgen05: second matrix")
         map_w2 = weight_map(w2)
+    if gate_form is not None:
+        # the gated epilogue takes no bias: the three constants of its form travel in that argument
+        _need(mode == ops.EPI_SILU_MUL and bias is None and gate_form.is_cuda and gate_form.dtype == torch.float32
+              and gate_form.numel() == 3, "gemm_tcgen05: a gate form is three float32 constants of the gated epilogue")
+        bias = gate_form
     if m == 0:
         return out
     tile, planned = plan(m, n, k, mode)

@@ -25,13 +25,18 @@ class GQAttention(Mixer):
     # `chunk` positions counted from the start of the sequence, a factor on the mixer's result
     # (`out_scale`, applied to the attention's output in float32 before the output projection), and
     # the tensors' names below the part's prefix (`names`: q, k, v, o and, with biases, q_bias, ...).
+    # `qk_norm_eps`: every q and k head is RMS-normalised before the rotation, with one weight of head_dim
+    # values for the q heads and one for the k heads (`names`: q_norm, k_norm).  `values_from_keys`: there is
+    # no value projection; a position's values are its keys as projected, before norm and rotation.
     _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-              "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias"}
+              "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
 
     def __init__(self, *, n_heads: int, n_kv_heads: int, head_dim: int, qkv_bias: bool,
                  position: PartSpec, window: int | None = None, v_head_dim: int | None = None,
                  scale: float | None = None, chunk: int | None = None, out_scale: float = 1.0,
-                 names: dict | None = None, hidden_size: int, dtype, device):
+                 names: dict | None = None, qk_norm_eps: float | None = None, values_from_keys: bool = False,
+                 hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
@@ -39,9 +44,18 @@ class GQAttention(Mixer):
             raise ValueError(f"a chunk holds at least one position, found {chunk}")
         self.n_heads, self.n_kv_heads, self.head_dim = n_heads, n_kv_heads, head_dim
         self.v_head_dim = head_dim if v_head_dim is None else int(v_head_dim)
+        self.values_from_keys = bool(values_from_keys)
+        if self.values_from_keys and self.v_head_dim != head_dim:
+            raise ValueError(f"values taken from keys of size {head_dim} cannot have the size {self.v_head_dim}")
+        if window is not None and window <= 0:
+            raise ValueError(f"a window holds at least one position, found {window}")
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.q_dim, self.kv_dim = n_heads * head_dim, n_kv_heads * head_dim
         self.v_dim, self.o_dim = n_kv_heads * self.v_head_dim, n_heads * self.v_head_dim
         self.qkv_bias = bool(qkv_bias)
+        if self.values_from_keys and self.qkv_bias:
+            raise ValueError("values taken from keys and projection biases are not combined")
+        self.q_norm = self.k_norm = None
         self.window = window
         self.chunk = chunk
         self.out_scale = float(out_scale)
@@ -59,6 +73,11 @@ class GQAttention(Mixer):
             nm["v"]: TensorSpec((self.v_dim, h)),
             nm["o"]: TensorSpec((h, self.o_dim)),
         }
+        if self.values_from_keys:
+            del specs[nm["v"]]
+        if self.qk_norm_eps is not None:
+            specs[nm["q_norm"]] = TensorSpec((self.head_dim,), role="vector", init="ones")
+            specs[nm["k_norm"]] = TensorSpec((self.head_dim,), role="vector", init="ones")
         if self.qkv_bias:
             specs[nm["q_bias"]] = TensorSpec((self.q_dim,), role="vector")
             specs[nm["k_bias"]] = TensorSpec((self.kv_dim,), role="vector")
@@ -68,7 +87,10 @@ class GQAttention(Mixer):
     def set_tensors(self, tensors):
         nm = self.names
         # one matrix for the three projections: one pass over x
-        self.w_qkv = linear.Weight(torch.cat([tensors[nm["q"]], tensors[nm["k"]], tensors[nm["v"]]], dim=0))
+        mats = [tensors[nm["q"]], tensors[nm["k"]]] + ([] if self.values_from_keys else [tensors[nm["v"]]])
+        self.w_qkv = linear.Weight(torch.cat(mats, dim=0))
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[nm["q_norm"]].contiguous(), tensors[nm["k_norm"]].contiguous()
         if self.qkv_bias:
             self.b_qkv = torch.cat([tensors[nm["q_bias"]], tensors[nm["k_bias"]], tensors[nm["v_bias"]]],
                                    dim=0).contiguous()
@@ -78,6 +100,10 @@ class GQAttention(Mixer):
         q, kv, nm = self.q_dim, self.kv_dim, self.names
         w = self.w_qkv.t
         out = {nm["q"]: w[:q], nm["k"]: w[q:q + kv], nm["v"]: w[q + kv:], nm["o"]: self.w_o.t}
+        if self.values_from_keys:
+            del out[nm["v"]]
+        if self.qk_norm_eps is not None:
+            out[nm["q_norm"]], out[nm["k_norm"]] = self.q_norm, self.k_norm
         if self.qkv_bias:
             b = self.b_qkv
             out.update({nm["q_bias"]: b[:q], nm["k_bias"]: b[q:q + kv], nm["v_bias"]: b[q + kv:]})
@@ -92,8 +118,9 @@ class GQAttention(Mixer):
 
     def forward(self, x, residual, ctx, cache_layer, writes_cache):
         n = x.shape[0]
-        width = self.q_dim + self.kv_dim + self.v_dim
-        usual = self.v_head_dim == self.head_dim and not getattr(self.position, "partial", False)
+        width = self.q_dim + self.kv_dim + (0 if self.values_from_keys else self.v_dim)
+        special = self.values_from_keys or self.qk_norm_eps is not None
+        usual = self.v_head_dim == self.head_dim and not getattr(self.position, "partial", False) and not special
         from_acc = getattr(self.position, "apply_and_store_from_accumulators", None) if usual else None
         if from_acc is not None and linear.wants_split(x, self.w_qkv):
             # a small step: the projection is split over K into float32 accumulators, and the
@@ -107,9 +134,17 @@ class GQAttention(Mixer):
             qkv = ctx.buffer("qkv", (n, width), self.dtype)
             linear.project(x, self.w_qkv, qkv, ctx, bias=self.b_qkv)
             extra = {} if usual else {"v_head_dim": self.v_head_dim}
-            self.position.apply_and_store(qkv, ctx, cache_layer, n_heads=self.n_heads,
-                                          n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
-                                          write_kv=writes_cache, **extra)
+            if special:
+                # norm of the heads, rotation and cache write as one kernel (the position encoding's)
+                self.position.apply_normed_and_store(
+                    qkv, ctx, cache_layer, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
+                    write_kv=writes_cache, q_weight=self.q_norm, k_weight=self.k_norm,
+                    eps=self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
+                    values_from_keys=self.values_from_keys, **extra)
+            else:
+                self.position.apply_and_store(qkv, ctx, cache_layer, n_heads=self.n_heads,
+                                              n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
+                                              write_kv=writes_cache, **extra)
         mixed = ctx.buffer("attn_out", (n, self.o_dim), self.dtype)
         attn_kernels.attention(qkv, cache_layer, mixed, ctx, n_heads=self.n_heads,
                                n_kv_heads=self.n_kv_heads, head_dim=self.head_dim, scale=self.scale,

@@ -44,3 +44,19 @@ class ParallelTwoNorms(Arrangement):
         self.mixer.forward(normed, residual, ctx, cache_layer, writes_cache)
         if self.feed_forward is not None:
             self.feed_forward.forward(normed_ff, residual, ctx)
+
+
+@register("arrangement", "parallel_shared_norm")
+class ParallelSharedNorm(Arrangement):
+    """x <- x + (mixer(h) + ff(h)) with h = norm(x): one norm, and mixer and feed-forward both read its
+    output; both add onto the float32 stream.  A layer may have no feed-forward."""
+
+    ROLES = {"mixer": "mixer", "feed_forward": "feed_forward", "norm": "norm"}
+    OPTIONAL = ("feed_forward",)
+
+    def forward(self, residual, ctx, cache_layer, writes_cache):
+        normed = ctx.buffer("normed", (residual.shape[0], residual.shape[1]), ctx.dtype)
+        self.norm.forward(residual, normed)
+        self.mixer.forward(normed, residual, ctx, cache_layer, writes_cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(normed, residual, ctx)

@@ -1,4 +1,5 @@
-"""The token embedding: a row of the table per token, widened to float32 (transformer.rs:74-75)."""
+"""The token embedding: a row of the table per token, widened to float32 (transformer.rs:74-75), times a
+factor when the model has one (the table itself stays unscaled: a tied head reads it as it is)."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -9,9 +10,10 @@ from .spec import TensorSpec
 
 @register("embedding", "token_embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, *, vocab_size: int, weight_name: str = "weight", hidden_size: int, dtype, device):
+    def __init__(self, *, vocab_size: int, weight_name: str = "weight", scale: float = 1.0, hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         self.vocab_size = vocab_size
+        self.scale = float(scale)           # on the rows as they enter the float32 stream
         self.weight_name = weight_name      # the table's name below the part's prefix
         self.weight = None
 
@@ -28,4 +30,4 @@ class TokenEmbedding(Embedding):
         return self.weight
 
     def forward(self, ctx, residual):
-        ops.embed_gather(self.weight, ctx.token_ids, residual)
+        ops.embed_gather(self.weight, ctx.token_ids, residual, self.scale)

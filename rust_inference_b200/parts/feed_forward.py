@@ -1,4 +1,5 @@
-"""SwiGLU feed-forward (mlp.rs:31-46): down( silu(gate x) * (up x) ), no biases."""
+"""Gated feed-forwards without biases: SwiGLU (mlp.rs:31-46), down( silu(gate x) * (up x) ), and the bounded
+form down( g sigmoid(alpha g) (u + shift) ) with g = min(gate x, limit), u = clamp(up x, -limit, limit)."""
 from __future__ import annotations
 
 import torch
@@ -37,4 +38,43 @@ class SwiGLU(FeedForward):
         # gate and up in one pass over x, SiLU-gate in the epilogue (mlp.rs:35-43)
         linear.gated(x, self.w_gate, self.w_up, act, ctx)
         # down projection added onto the residual stream (mlp.rs:45, transformer.rs:47)
+        linear.into_residual(act, self.w_down, residual, ctx)
+
+
+@register("feed_forward", "bounded_glu")
+class BoundedGLU(FeedForward):
+    """y = g * sigmoid(alpha * g) * (u + shift) with g = min(W_gate x, limit) and u = clamp(W_up x, -limit, limit);
+    out = W_down y.  The activation is the gated epilogue of the gate / up contraction with these three
+    constants (float32 arithmetic on the accumulators).  `names`: gate, up, down below the part's prefix."""
+
+    _NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    def __init__(self, *, intermediate_size: int, limit: float, alpha: float = 1.702, shift: float = 1.0,
+                 names: dict | None = None, hidden_size: int, dtype, device):
+        super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+        if not limit > 0:
+            raise ValueError(f"the bound of a bounded gate is positive, found {limit}")
+        self.intermediate_size = intermediate_size
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.names = dict(self._NAMES, **(names or {}))
+        self.form = torch.tensor([self.alpha, self.limit, self.shift], dtype=torch.float32, device=self.device)
+        self.w_gate = self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        i, h, nm = self.intermediate_size, self.hidden_size, self.names
+        return {nm["gate"]: TensorSpec((i, h)), nm["up"]: TensorSpec((i, h)), nm["down"]: TensorSpec((h, i))}
+
+    def set_tensors(self, tensors):
+        nm = self.names
+        self.w_gate = linear.Weight(tensors[nm["gate"]])
+        self.w_up = linear.Weight(tensors[nm["up"]])
+        self.w_down = linear.Weight(tensors[nm["down"]])
+
+    def get_tensors(self):
+        nm = self.names
+        return {nm["gate"]: self.w_gate.t, nm["up"]: self.w_up.t, nm["down"]: self.w_down.t}
+
+    def forward(self, x, residual, ctx):
+        act = ctx.buffer("ffn_act", (x.shape[0], self.intermediate_size), self.dtype)
+        linear.gated(x, self.w_gate, self.w_up, act, ctx, form=self.form)
         linear.into_residual(act, self.w_down, residual, ctx)

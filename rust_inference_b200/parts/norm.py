@@ -48,3 +48,27 @@ class RMSNorm(Norm):
             return False
         ops.rmsnorm_pair(x, self.factor, other.factor, self.eps, out, out_other)
         return True
+
+
+@register("norm", "layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * weight, var the mean of the squared deviations; no bias;
+    statistics in float32.  `weight_name` is the tensor's name below the part's prefix."""
+
+    def __init__(self, *, eps: float, weight_name: str = "weight", hidden_size: int, dtype, device):
+        super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
+        self.eps = float(eps)
+        self.weight_name = weight_name
+        self.weight = None
+
+    def tensor_specs(self):
+        return {self.weight_name: TensorSpec((self.hidden_size,), role="vector", init="ones")}
+
+    def set_tensors(self, tensors):
+        self.weight = tensors[self.weight_name]
+
+    def get_tensors(self):
+        return {self.weight_name: self.weight}
+
+    def forward(self, x, out, rows=None):
+        return ops.layernorm(x, self.weight, self.eps, out, rows)

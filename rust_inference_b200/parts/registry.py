@@ -53,4 +53,4 @@ def kinds(category: str) -> list[str]:
 
 def _ensure_builtin() -> None:
     from . import norm, rope, attention, feed_forward, block, embedding, head  # noqa: F401
-    from . import recurrence, parallel_mixer, routed_experts  # noqa: F401
+    from . import recurrence, parallel_mixer, routed_experts, latent_attention  # noqa: F401

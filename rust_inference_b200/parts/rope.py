@@ -11,19 +11,22 @@ from .registry import register
 _STYLES = {"half": 0, "interleaved": 1}
 
 
-def rope_tables(head_dim: int, base: float, n_positions: int, exact_angles: bool = False):
+def rope_tables(head_dim: int, base: float, n_positions: int, exact_angles: bool = False, scaling_factor: float = 1.0):
     """cos, sin as float32 [n_positions, head_dim/2], built the way rope.rs:47-55 does:
     exponent = 2i/dim, theta = 1/base^exponent and angle = pos*theta are 32-bit numbers
     (the power is taken in float64 and rounded once); cos and sin are taken of the 32-bit
     angle in float64 and rounded once.  With exact_angles frequency and angle stay float64 and
-    only cos and sin are rounded."""
+    only cos and sin are rounded.  Every frequency is divided by scaling_factor (linear position scaling)."""
     half = head_dim // 2
     if exact_angles:
         theta = np.power(np.float64(base), -2.0 * np.arange(half, dtype=np.float64) / np.float64(head_dim))
+        theta = theta / np.float64(scaling_factor)
         angle = np.arange(n_positions, dtype=np.float64)[:, None] * theta[None, :]
         return np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
     exponent = (2 * np.arange(half)).astype(np.float32) / np.float32(head_dim)
     theta = (1.0 / np.power(np.float64(np.float32(base)), exponent.astype(np.float64))).astype(np.float32)
+    if scaling_factor != 1.0:
+        theta = (theta / np.float32(scaling_factor)).astype(np.float32)
     pos = np.arange(n_positions, dtype=np.float32)
     angle = (pos[:, None] * theta[None, :]).astype(np.float32)
     cos = np.cos(angle.astype(np.float64)).astype(np.float32)
@@ -37,10 +40,10 @@ class RotaryEncoding(PositionEncoding):
     position (attention.rs:78-87); v is not rotated.  style "interleaved" pairs (2i, 2i+1)
     as rope.rs:92-96 does; "half" pairs (i, i + dim/2).  `rot_dims` < head_dim rotates only
     the first rot_dims channels of every head (frequencies base^(-2i/rot_dims), pairs within
-    them) and lets the rest pass."""
+    them) and lets the rest pass.  `scaling_factor` divides every frequency (linear position scaling)."""
 
     def __init__(self, *, head_dim: int, base: float, style: str = "half", rot_dims: int | None = None,
-                 exact_angles: bool = False, hidden_size: int, dtype, device):
+                 exact_angles: bool = False, scaling_factor: float = 1.0, hidden_size: int, dtype, device):
         super().__init__(hidden_size=hidden_size, dtype=dtype, device=device)
         if style not in _STYLES:
             raise ValueError(f"rope style must be one of {sorted(_STYLES)}, found {style!r}")
@@ -52,6 +55,9 @@ class RotaryEncoding(PositionEncoding):
         self.base = float(base)
         self.style = _STYLES[style]
         self.exact_angles = bool(exact_angles)
+        self.scaling_factor = float(scaling_factor)
+        if not self.scaling_factor > 0:
+            raise ValueError(f"a rope scaling factor is positive, found {scaling_factor}")
         self.cos = self.sin = None
 
     @property
@@ -60,7 +66,7 @@ class RotaryEncoding(PositionEncoding):
 
     def prepare(self, max_positions: int) -> None:
         if self.cos is None or self.cos.shape[0] < max_positions:
-            cos, sin = rope_tables(self.rot_dims, self.base, max_positions, self.exact_angles)
+            cos, sin = rope_tables(self.rot_dims, self.base, max_positions, self.exact_angles, self.scaling_factor)
             self.cos = torch.from_numpy(cos).contiguous().to(self.device)
             self.sin = torch.from_numpy(sin).contiguous().to(self.device)
 
@@ -71,6 +77,18 @@ class RotaryEncoding(PositionEncoding):
                              ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads,
                              n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size,
                              style=self.style, write_kv=write_kv, rot_dims=self.rot_dims, v_head_dim=v_head_dim)
+
+    def apply_normed_and_store(self, qkv, ctx, cache_layer, *, n_heads, n_kv_heads, head_dim, write_kv, q_weight,
+                               k_weight, eps, values_from_keys=False, v_head_dim=None):
+        """The same after an RMS norm of every q and k head (weights shared by the heads; None: no norm); with
+        values_from_keys the cached values are the keys as projected, before norm and rotation."""
+        if self.cos is None or self.cos.shape[0] < ctx.max_len:
+            raise RuntimeError("rope tables do not cover the step's positions; call prepare() first")
+        ops.rope_normed_cache_write(qkv, self.cos, self.sin, q_weight, k_weight, eps, ctx.token_pos, ctx.token_seq,
+                                    ctx.seq_slot, ctx.page_table, cache_layer.k, cache_layer.v, n_heads=n_heads,
+                                    n_kv_heads=n_kv_heads, head_dim=head_dim, page_size=ctx.page_size, style=self.style,
+                                    write_kv=write_kv, rot_dims=self.rot_dims, v_head_dim=v_head_dim,
+                                    values_from_keys=values_from_keys)
 
     def apply_and_store_from_accumulators(self, acc, bias, q_out, ctx, cache_layer, *, n_heads, n_kv_heads,
                                           head_dim, write_kv):
