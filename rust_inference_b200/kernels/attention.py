@@ -131,10 +131,38 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
         v_head_dim=v_head_dim, out_scale=out_scale)
 
 
+# RI_B200_LATENT_ATTENTION=generic keeps the generic kernel for attention over a shared latent (for comparisons)
+_LATENT = os.environ.get("RI_B200_LATENT_ATTENTION", "mma")
+LATENT_TILE_ROWS, LATENT_TILE_KEYS, LATENT_MAX_SPLITS = 64, 32, 16
+
+
+def latent_splits(n_ctas: int, longest: int) -> int:
+    """Runs of keys per sequence for a step whose row tiles alone make n_ctas CTAs: as many as fill the SMs once
+    (the kernel holds one CTA per SM), never more than the longest sequence has key tiles."""
+    return max(1, min(LATENT_MAX_SPLITS, _sm_count() // max(1, n_ctas), -(-longest // LATENT_TILE_KEYS)))
+
+
 def latent_attention(q_wide, cache_layer, out, ctx, *, n_heads, key_dim, rank, scale):
     """Attention of n_heads query heads over ONE kv head whose keys are the cached rows [key_dim] and whose
     values are the rows' first `rank` channels (no storage of their own); causal.  q_wide is
-    [T, n_heads * key_dim]; out is head-major, [n_heads, T, rank]."""
+    [T, n_heads * key_dim]; out is head-major, [n_heads, T, rank].  bfloat16 with a latent the tensor-core kernel
+    is built for: `latent_attention_mma` (steps of few rows cut the keys into runs); anything else: the generic
+    kernel."""
+    rd = key_dim - rank
+    if q_wide.dtype == torch.bfloat16 and _LATENT != "generic" and ops.latent_attention_mma_supports(rank, rd, ctx.page_size):
+        n = q_wide.shape[0]
+        halves = 2 if rank > 256 else 1
+        tiles = -(-(ctx.max_new * n_heads) // LATENT_TILE_ROWS)
+        # a decode step's grid may depend on the batch size and the cache geometry only (captured steps)
+        longest = ctx.page_table.shape[1] * ctx.page_size if ctx.all_single else ctx.max_len
+        splits = latent_splits(tiles * ctx.n_seqs * halves, longest)
+        part_o = part_ml = None
+        if splits > 1:
+            part_o = ctx.buffer("latent_part_o", (n * n_heads * splits * rank,), torch.float32)
+            part_ml = ctx.buffer("latent_part_ml", (n * n_heads * splits * 2,), torch.float32)
+        return ops.latent_attention_mma(q_wide, cache_layer.k, ctx.page_table, ctx.seq_slot, ctx.seq_start, ctx.cu_seqlens,
+                                        out, n_seqs=ctx.n_seqs, max_new=ctx.max_new, n_heads=n_heads, rank=rank, rot_dim=rd,
+                                        scale=scale, n_splits=splits, part_o=part_o, part_ml=part_ml)
     return ops.attention_generic(
         q_wide, q_wide.shape[1], cache_layer.k, cache_layer.k, ctx.page_table, ctx.token_pos, ctx.token_seq,
         ctx.seq_slot, out, n_tokens=q_wide.shape[0], n_heads=n_heads, n_kv_heads=1, head_dim=key_dim,

@@ -34,6 +34,7 @@ MODULES = {
     "moe": "moe.cu",
     "moe_tcgen05": "moe_tcgen05.cu",
     "latent": "latent.cu",
+    "latent_attention_mma": "latent_attention_mma.cu",
     "wait_probe": "wait_probe.cu",
     "host_runtime": "host_runtime.cpp",
 }

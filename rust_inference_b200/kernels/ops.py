@@ -740,3 +740,35 @@ def latent_gate(v: torch.Tensor, gates: torch.Tensor | None, out: torch.Tensor, 
         ld = gates.stride(0)
     _call("latent", "ri_latent_gate", _p(v), _p(gates), c_int(ld), _p(out), c_int(dtype_code(out.dtype)), c_int(n_tokens),
           c_int(n_heads), c_int(v_head_dim), _stream())
+
+
+def latent_attention_mma_supports(rank: int, rot_dim: int, page_size: int) -> bool:
+    return bool(load("latent_attention_mma").ri_latent_attention_mma_supports(c_int(rank), c_int(rot_dim), c_int(page_size)))
+
+
+def latent_attention_mma(q_wide: torch.Tensor, cache: torch.Tensor, page_table, seq_slot, seq_start, cu_seqlens,
+                         out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, rank: int, rot_dim: int, scale: float,
+                         n_splits: int = 1, part_o: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of n_heads query heads over one cached row per position on the tensor cores (bfloat16):
+    q_wide [T, n_heads * (rank + rot_dim)], cache [pages, 1, 64, rank + rot_dim] (keys: the rows; values: their
+    first `rank` channels), out head-major [n_heads, T, rank].  n_splits > 1 cuts every sequence's keys into runs
+    whose partial results (part_o float32 [T * n_heads * n_splits * rank], part_ml float32 [T * n_heads * n_splits
+    * 2]) a second kernel merges."""
+    _need_cuda(q_wide, cache, page_table, seq_slot, seq_start, cu_seqlens, out, part_o, part_ml)
+    n = q_wide.shape[0]
+    wide = rank + rot_dim
+    _need(q_wide.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+          and q_wide.is_contiguous() and cache.is_contiguous() and out.is_contiguous(), "latent_attention: bfloat16, contiguous")
+    _need(q_wide.shape[1] == n_heads * wide and tuple(cache.shape[1:]) == (1, 64, wide) and out.numel() == n * n_heads * rank,
+          "latent_attention: shapes")
+    if n_splits > 1:
+        _need(part_o is not None and part_ml is not None and part_o.dtype == torch.float32 and part_ml.dtype == torch.float32
+              and part_o.numel() >= n * n_heads * n_splits * rank and part_ml.numel() >= n * n_heads * n_splits * 2,
+              "latent_attention: scratch for the runs' partial results")
+    _call("latent_attention_mma", "ri_latent_attention_mma", _p(q_wide), _p(cache), _p(page_table), c_int(page_table.shape[1]),
+          _p(seq_slot), _p(seq_start), _p(cu_seqlens), c_int(n_seqs), c_int(max_new), c_int(n_heads), c_int(n), c_int(rank),
+          c_int(rot_dim), c_float(scale), c_int(n_splits), _p(part_o), _p(part_ml), _p(out), _stream())
+    if n_splits > 1:
+        global _launches
+        _launches += 1                       # the merge is a kernel of its own
+    return out

@@ -535,3 +535,78 @@ def test_the_command_line_on_a_vadodra_folder(models, tmp_path):
                         "-n", "5", "--max-seq-len", "128", "--dump-layer-stats"], capture_output=True, text=True, timeout=900)
     assert p.returncode == 0, p.stderr[-2000:]
     assert len([l for l in p.stdout.splitlines() if l.strip()]) == 2 and "[L4]" in p.stderr + p.stdout
+
+
+@pytest.mark.parametrize("rank,rd,heads", [(64, 32, 8), (128, 64, 3), (256, 32, 5), (512, 64, 16), (512, 32, 1), (64, 64, 128)])
+def test_latent_attention_on_tensor_cores(rank, rd, heads):
+    """The tensor-core kernel of attention over one cached row per position against plain softmax attention over the
+    same rows: prompts of unequal length in one step (row tiles that end inside a token's heads), a continuation by a
+    portion, decoding with the keys cut into runs that are merged, pages out of order; one cached row made so that
+    its score dwarfs the others for one head, at the first position, at a page border, and just behind the
+    last query that may see it."""
+    from rust_inference_b200.kernels import attention as attn_kernels, ops
+    assert ops.latent_attention_mma_supports(rank, rd, 64)
+    g = torch.Generator().manual_seed(rank + rd + heads)
+    page, wide = 64, rank + rd
+    lens = [200, 70, 33]
+    n_pages = 12
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(4, 5, dtype=torch.int32)
+    rows, at = [], 0
+    for b, n in enumerate(lens):
+        for k in range(-(-n // page)):
+            table[b + 1, k] = perm[at]                                   # slots 1..3
+            at += 1
+        rows.append((torch.randn(n, wide, generator=g) * 0.5).to(torch.bfloat16))
+    scale = 0.5 / math.sqrt(wide)
+    cache = torch.zeros(n_pages, 1, page, wide, dtype=torch.bfloat16)
+    for b, n in enumerate(lens):
+        for p in range(n):
+            cache[table[b + 1, p // page], 0, p % page] = rows[b][p]
+    qs = [(torch.randn(n, heads, wide, generator=g) * 0.5).to(torch.bfloat16) for n in lens]
+    # a key that one head's queries love: the query points along it
+    for b, special in ((0, 0), (0, 64), (1, 63), (2, 20)):
+        rows_b = rows[b]
+        h = special % heads
+        qs[b][:, h] = (rows_b[special].float() * (30.0 / (scale * float(rows_b[special].float().pow(2).sum())))).to(torch.bfloat16)
+    dcache = d(cache)
+
+    def plain(b, lo, hi):
+        k = rows[b].double()
+        s = torch.einsum("ihd,jd->hij", qs[b][lo:hi].double(), k) * scale
+        pos = torch.arange(lo, hi)
+        s = s.masked_fill((pos[:, None] < torch.arange(lens[b])[None, :])[None], float("-inf"))
+        return torch.einsum("hij,jr->hir", torch.softmax(s, -1), k[:, :rank])        # [heads, tokens, rank]
+
+    class Ctx:
+        pass
+
+    def run(seqs, starts, counts):
+        ctx = Ctx()
+        ctx.n_seqs, ctx.max_new, ctx.page_size = len(seqs), max(counts), page
+        ctx.all_single = all(c == 1 for c in counts)
+        ctx.max_len = max(s + c for s, c in zip(starts, counts))
+        ctx.page_table = d(table)
+        ctx.seq_slot, ctx.seq_start = i32([b + 1 for b in seqs]), i32(starts)
+        ctx.cu_seqlens = i32([0] + torch.tensor(counts).cumsum(0).tolist())
+        ctx.token_pos = i32([s + i for s, c in zip(starts, counts) for i in range(c)])
+        ctx.token_seq = i32([k for k, c in enumerate(counts) for _ in range(c)])
+        bufs = {}
+        ctx.buffer = lambda name, shape, dtype: bufs.setdefault((name, shape), torch.empty(shape, dtype=dtype, device=DEV))
+        q = torch.cat([qs[b][s:s + c] for b, s, c in zip(seqs, starts, counts)]).reshape(-1, heads * wide)
+        n = q.shape[0]
+        out = torch.empty(heads, n, rank, dtype=torch.bfloat16, device=DEV)
+        attn_kernels.latent_attention(d(q), type("L", (), {"k": dcache}), out, ctx, n_heads=heads, key_dim=wide, rank=rank,
+                                      scale=scale)
+        ref = torch.empty_like(out)
+        ops.attention_generic(d(q), heads * wide, dcache, dcache, ctx.page_table, ctx.token_pos, ctx.token_seq, ctx.seq_slot, ref,
+                              n_tokens=n, n_heads=heads, n_kv_heads=1, head_dim=wide, page_size=page, scale=scale,
+                              v_head_dim=rank, values_in_keys=True, head_major=True)
+        want = torch.cat([plain(b, s, s + c) for b, s, c in zip(seqs, starts, counts)], dim=1)
+        assert rel_err(out.reshape(-1, rank), want.reshape(-1, rank)) < 2e-2, (seqs, starts, counts)
+        assert rel_err(out.reshape(-1, rank), ref.float().reshape(-1, rank)) < 2e-2
+
+    run([0, 1, 2], [0, 0, 0], lens)                       # whole prompts
+    run([0, 1], [150, 64], [50, 6])                       # continuations by portions
+    run([1, 0, 2], [69, 199, 32], [1, 1, 1])              # decoding, the keys in runs
+    run([2], [0], [1])                                    # the first token of a sequence alone
