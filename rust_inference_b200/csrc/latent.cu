@@ -103,9 +103,25 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restric
 
 template <typename T>
 __global__ void latent_widen_kernel(const float* __restrict__ q_lat, T* __restrict__ q_wide, int n_tokens, int n_heads,
-                                    int rank, int rd) {
+                                    int rank, int rd, int vec) {
     let_next_kernel_start();
     wait_for_previous_kernels();
+    if (vec) {                      // bf16, rank and rd multiples of 8: eight channels per thread, 16-byte stores
+        const int r8 = rank >> 3;
+        const size_t total = (size_t)n_tokens * n_heads * r8;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const int j = (int)(i % r8) * 8;
+            const size_t th = i / r8;
+            const int h = (int)(th % n_heads);
+            const size_t t = th / n_heads;
+            const float4* src = reinterpret_cast<const float4*>(q_lat + ((size_t)h * n_tokens + t) * rank + j);
+            const float4 a = src[0], b = src[1];
+            __nv_bfloat162 p[4] = {__floats2bfloat162_rn(a.x, a.y), __floats2bfloat162_rn(a.z, a.w),
+                                   __floats2bfloat162_rn(b.x, b.y), __floats2bfloat162_rn(b.z, b.w)};
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(q_wide) + th * (rank + rd) + j) = *reinterpret_cast<uint4*>(p);
+        }
+        return;
+    }
     const size_t total = (size_t)n_tokens * n_heads * rank;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int j = (int)(i % rank);
@@ -118,9 +134,27 @@ __global__ void latent_widen_kernel(const float* __restrict__ q_lat, T* __restri
 
 template <typename T>
 __global__ void latent_gate_kernel(const float* __restrict__ v, const T* __restrict__ gates, int gate_ld,
-                                   T* __restrict__ out, int n_tokens, int n_heads, int vd) {
+                                   T* __restrict__ out, int n_tokens, int n_heads, int vd, int vec) {
     let_next_kernel_start();
     wait_for_previous_kernels();
+    if (vec) {                      // bf16, vd a multiple of 8: eight channels per thread, 16-byte stores
+        const int v8 = vd >> 3;
+        const size_t total = (size_t)n_tokens * n_heads * v8;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const int j = (int)(i % v8) * 8;
+            const size_t th = i / v8;
+            const int h = (int)(th % n_heads);
+            const size_t t = th / n_heads;
+            float g = 1.f;
+            if (gates != nullptr) g = 1.f / (1.f + expf(-to_f32<T>(gates[t * gate_ld + h])));
+            const float4* src = reinterpret_cast<const float4*>(v + ((size_t)h * n_tokens + t) * vd + j);
+            const float4 a = src[0], b = src[1];
+            __nv_bfloat162 p[4] = {__floats2bfloat162_rn(a.x * g, a.y * g), __floats2bfloat162_rn(a.z * g, a.w * g),
+                                   __floats2bfloat162_rn(b.x * g, b.y * g), __floats2bfloat162_rn(b.z * g, b.w * g)};
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + th * vd + j) = *reinterpret_cast<uint4*>(p);
+        }
+        return;
+    }
     const size_t total = (size_t)n_tokens * n_heads * vd;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const int j = (int)(i % vd);
@@ -169,10 +203,11 @@ RI_API int ri_latent_prepare(const void* proj, int dtype, int ld, const float* c
 RI_API int ri_latent_widen(const float* q_lat, void* q_wide, int dtype, int n_tokens, int n_heads, int rank, int rd,
                            cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    const int blocks = blocks_for((size_t)n_tokens * n_heads * rank);
+    const int vec = dtype == RI_BF16 && rank % 8 == 0 && rd % 8 == 0 && (uintptr_t)q_lat % 16 == 0 && (uintptr_t)q_wide % 16 == 0;
+    const int blocks = blocks_for((size_t)n_tokens * n_heads * rank / (vec ? 8 : 1));
     cudaError_t e;
-    if (dtype == RI_F32) e = launch_dependent(latent_widen_kernel<float>, blocks, 256, 0, stream, q_lat, (float*)q_wide, n_tokens, n_heads, rank, rd);
-    else if (dtype == RI_BF16) e = launch_dependent(latent_widen_kernel<__nv_bfloat16>, blocks, 256, 0, stream, q_lat, (__nv_bfloat16*)q_wide, n_tokens, n_heads, rank, rd);
+    if (dtype == RI_F32) e = launch_dependent(latent_widen_kernel<float>, blocks, 256, 0, stream, q_lat, (float*)q_wide, n_tokens, n_heads, rank, rd, 0);
+    else if (dtype == RI_BF16) e = launch_dependent(latent_widen_kernel<__nv_bfloat16>, blocks, 256, 0, stream, q_lat, (__nv_bfloat16*)q_wide, n_tokens, n_heads, rank, rd, vec);
     else return fail("latent_widen: unknown dtype %d", dtype);
     return check_launch(e, "latent_widen");
 }
@@ -180,10 +215,11 @@ RI_API int ri_latent_widen(const float* q_lat, void* q_wide, int dtype, int n_to
 RI_API int ri_latent_gate(const float* v, const void* gates, int gate_ld, void* out, int dtype, int n_tokens, int n_heads,
                           int vd, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    const int blocks = blocks_for((size_t)n_tokens * n_heads * vd);
+    const int vec = dtype == RI_BF16 && vd % 8 == 0 && (uintptr_t)v % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int blocks = blocks_for((size_t)n_tokens * n_heads * vd / (vec ? 8 : 1));
     cudaError_t e;
-    if (dtype == RI_F32) e = launch_dependent(latent_gate_kernel<float>, blocks, 256, 0, stream, v, (const float*)gates, gate_ld, (float*)out, n_tokens, n_heads, vd);
-    else if (dtype == RI_BF16) e = launch_dependent(latent_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, v, (const __nv_bfloat16*)gates, gate_ld, (__nv_bfloat16*)out, n_tokens, n_heads, vd);
+    if (dtype == RI_F32) e = launch_dependent(latent_gate_kernel<float>, blocks, 256, 0, stream, v, (const float*)gates, gate_ld, (float*)out, n_tokens, n_heads, vd, 0);
+    else if (dtype == RI_BF16) e = launch_dependent(latent_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, v, (const __nv_bfloat16*)gates, gate_ld, (__nv_bfloat16*)out, n_tokens, n_heads, vd, vec);
     else return fail("latent_gate: unknown dtype %d", dtype);
     return check_launch(e, "latent_gate");
 }

@@ -4,8 +4,9 @@
 // A position's cached row holds KD = RANK + RD channels; it is the key of every head, and its first RANK
 // channels are the value of every head.  The queries come as rows of KD channels, one per (token, head), token
 // by token: row t * heads + h.  Because all heads read the same keys, the heads of a token (and of its
-// neighbours) are simply more query ROWS of one problem: a CTA takes 64 consecutive rows of one sequence, a warp
-// 16 of them, and walks the sequence's keys 32 at a time (half a cache page), causal per row.  Shapes per warp
+// neighbours) are simply more query ROWS of one problem: a CTA takes BM = 128 consecutive rows of one sequence
+// (64 when the step's sequences bring fewer), a warp 16 of them, and walks the sequence's keys 32 at a time
+// (half a cache page), causal per row.  Shapes per warp
 // and key tile: S[16 x 32] = Q[16 x KD] K^T (KD / 16 k-steps), then O[16 x NV] += P[16 x 32] V[32 x NV].
 //
 // NV is what a thread can hold of O in registers: 256 value channels (128 registers).  A latent of 512 channels
@@ -25,9 +26,7 @@ using namespace ri;
 namespace {
 
 constexpr int PAGE = 64;
-constexpr int BM = 64;              // query rows per CTA
 constexpr int BN = 32;              // keys per tile
-constexpr int THREADS = 128;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -55,8 +54,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int RANK, int RD, int NZ>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int RANK, int RD, int NZ, int BM>
+__global__ void __launch_bounds__(BM * 2, 1)
 latent_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                    const int* __restrict__ page_table, int max_pages, const int* __restrict__ seq_slot,
                    const int* __restrict__ seq_start, const int* __restrict__ cu_seqlens, int n_heads, int n_tokens,
@@ -66,6 +65,7 @@ latent_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     constexpr int ROW = (KD + 8) * 2;                 // bytes of a padded row in shared memory
     constexpr int NV = RANK / NZ;                     // value channels of this CTA
     constexpr int KSTEPS = KD / 16, NT_O = NV / 8;
+    constexpr int THREADS = BM * 2;                   // a warp per 16 rows
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t q_s = smem_u32(smem);              // [BM][KD + 8]
     const uint32_t k_s = q_s + BM * ROW;              // 2 x [BN][KD + 8]
@@ -254,19 +254,20 @@ __global__ void latent_attn_combine_kernel(const float* __restrict__ part_o, con
     }
 }
 
-template <int RANK, int RD>
+template <int RANK, int RD, int BM>
 int launch(const void* q, const void* cache, const int* page_table, int max_pages, const int* seq_slot, const int* seq_start,
            const int* cu_seqlens, int n_seqs, int max_new, int n_heads, int n_tokens, float scale, int n_splits, float* part_o,
            float* part_ml, void* out, cudaStream_t stream) {
     constexpr int NZ = RANK > 256 ? 2 : 1;
     constexpr int KD = RANK + RD;
     constexpr int SMEM = (BM + 2 * BN) * (KD + 8) * 2;
-    auto kernel = latent_attn_kernel<RANK, RD, NZ>;
+    static_assert(SMEM <= 227 * 1024, "the tile does not fit shared memory");
+    auto kernel = latent_attn_kernel<RANK, RD, NZ, BM>;
     static PerDeviceOnce configured;
     if (int rc = raise_dynamic_smem(kernel, SMEM, configured, "latent attention")) return rc;
     const int tiles = (int)(((long long)max_new * n_heads + BM - 1) / BM);
     dim3 grid(tiles, n_seqs * n_splits, NZ);
-    cudaError_t e = launch_dependent(kernel, grid, dim3(THREADS), (size_t)SMEM, stream, (const __nv_bfloat16*)q,
+    cudaError_t e = launch_dependent(kernel, grid, dim3(BM * 2), (size_t)SMEM, stream, (const __nv_bfloat16*)q,
                                      (const __nv_bfloat16*)cache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_heads,
                                      n_tokens, scale * 1.4426950408889634f, n_splits, part_o, part_ml, (__nv_bfloat16*)out);
     if (int rc = check_launch(e, "latent_attention")) return rc;
@@ -280,6 +281,9 @@ int launch(const void* q, const void* cache, const int* page_table, int max_page
 }
 
 }  // namespace
+
+// rows of queries a CTA takes in a step whose longest run of new rows is `rows` (the host plans its runs of keys with it)
+RI_API int ri_latent_attention_mma_tile_rows(long long rows) { return rows >= 128 ? 128 : 64; }
 
 // 1 if the kernel is built for these sizes (bf16 only; pages of 64 positions)
 RI_API int ri_latent_attention_mma_supports(int rank, int rd, int page_size) {
@@ -297,8 +301,12 @@ RI_API int ri_latent_attention_mma(const void* q, const void* cache, const int* 
     if (n_splits < 1 || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)))
         return fail("latent_attention: %d runs of keys need scratch for their partial results", n_splits);
     if ((long long)n_seqs * n_splits > 65535) return fail("latent_attention: %d sequences x %d runs exceed the grid limit", n_seqs, n_splits);
-#define RI_LATENT(R, D) if (rank == R && rd == D) return launch<R, D>(q, cache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, \
-        n_seqs, max_new, n_heads, n_tokens, scale, n_splits, part_o, part_ml, out, stream)
+    const bool big = ri_latent_attention_mma_tile_rows((long long)max_new * n_heads) == 128;
+#define RI_LATENT(R, D) if (rank == R && rd == D) return big \
+        ? launch<R, D, 128>(q, cache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads, n_tokens, scale, \
+                            n_splits, part_o, part_ml, out, stream) \
+        : launch<R, D, 64>(q, cache, page_table, max_pages, seq_slot, seq_start, cu_seqlens, n_seqs, max_new, n_heads, n_tokens, scale, \
+                           n_splits, part_o, part_ml, out, stream)
     RI_LATENT(64, 32); RI_LATENT(64, 64); RI_LATENT(128, 32); RI_LATENT(128, 64);
     RI_LATENT(256, 32); RI_LATENT(256, 64); RI_LATENT(512, 32); RI_LATENT(512, 64);
 #undef RI_LATENT

@@ -133,7 +133,7 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
 
 # RI_B200_LATENT_ATTENTION=generic keeps the generic kernel for attention over a shared latent (for comparisons)
 _LATENT = os.environ.get("RI_B200_LATENT_ATTENTION", "mma")
-LATENT_TILE_ROWS, LATENT_TILE_KEYS, LATENT_MAX_SPLITS = 64, 32, 16
+LATENT_TILE_KEYS, LATENT_MAX_SPLITS = 32, 16
 
 
 def latent_splits(n_ctas: int, longest: int) -> int:
@@ -152,7 +152,8 @@ def latent_attention(q_wide, cache_layer, out, ctx, *, n_heads, key_dim, rank, s
     if q_wide.dtype == torch.bfloat16 and _LATENT != "generic" and ops.latent_attention_mma_supports(rank, rd, ctx.page_size):
         n = q_wide.shape[0]
         halves = 2 if rank > 256 else 1
-        tiles = -(-(ctx.max_new * n_heads) // LATENT_TILE_ROWS)
+        rows = ctx.max_new * n_heads
+        tiles = -(-rows // (128 if rows >= 128 else 64))            # the kernel's row tile (ri_latent_attention_mma_tile_rows)
         # a decode step's grid may depend on the batch size and the cache geometry only (captured steps)
         longest = ctx.page_table.shape[1] * ctx.page_size if ctx.all_single else ctx.max_len
         splits = latent_splits(tiles * ctx.n_seqs * halves, longest)
