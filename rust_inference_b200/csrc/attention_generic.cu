@@ -25,7 +25,7 @@ using namespace ri;
 namespace {
 
 constexpr int THREADS = 128;
-constexpr int MAX_ACC = 4;          // head_dim <= THREADS * MAX_ACC
+constexpr int MAX_ACC = 8;          // value head size <= THREADS * MAX_ACC
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS)

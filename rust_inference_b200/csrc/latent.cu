@@ -24,6 +24,9 @@ using namespace ri;
 
 namespace {
 
+constexpr int PREPARE_HEADS = 4;    // query heads per block of the preparing kernel
+
+// grid (tokens, groups of PREPARE_HEADS heads); the first group's block also writes the cache row and the lists
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -32,9 +35,10 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restric
                       const int* __restrict__ page_table, int max_pages, T* __restrict__ cache, T* __restrict__ q_nope,
                       T* __restrict__ q_wide, int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ tiles,
                       int* __restrict__ n_tiles, int n_tokens, int n_heads, int d, int rd, int rank, int rot, int style,
-                      int page_size, int write_kv, int tile_rows) {
+                      int page_size, int write_kv, int tile_rows, int vec) {
     __shared__ float scratch[33];
     const int t = blockIdx.x, tid = threadIdx.x;
+    const int h0 = blockIdx.y * PREPARE_HEADS, nh = min(PREPARE_HEADS, n_heads - h0);
     const int pos = token_pos[t];                     // positions and tables: fixed before the step
     const int half = rot >> 1;
     const float* c = cos_t + (size_t)pos * half;
@@ -43,6 +47,34 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restric
     wait_for_previous_kernels();                      // the projection; and the lists may still be read by the layer before
     const T* row = proj + (size_t)t * ld;
     const int qh = d + rd, wide = rank + rd;
+
+    // queries: the unrotated parts head by head, the rotated parts into the wide rows
+    if (vec) {                                        // 2-byte values, 16 bytes at a time
+        const int d8 = d >> 3;
+        for (int i = tid; i < nh * d8; i += blockDim.x) {
+            const int h = h0 + i / d8, j = (i % d8) * 8;
+            *reinterpret_cast<uint4*>(q_nope + ((size_t)h * n_tokens + t) * d + j) = *reinterpret_cast<const uint4*>(row + h * qh + j);
+        }
+    } else {
+        for (int i = tid; i < nh * d; i += blockDim.x) {
+            const int h = h0 + i / d, j = i % d;
+            q_nope[((size_t)h * n_tokens + t) * d + j] = row[h * qh + j];
+        }
+    }
+    for (int i = tid; i < nh * half; i += blockDim.x) {
+        const int h = h0 + i / half, k = i % half;
+        const int i0 = style == 0 ? k : 2 * k, i1 = style == 0 ? k + half : 2 * k + 1;
+        const T* v = row + h * qh + d;
+        const float x0 = to_f32<T>(v[i0]), x1 = to_f32<T>(v[i1]);
+        T* dst = q_wide + ((size_t)t * n_heads + h) * wide + rank;
+        dst[i0] = from_f32<T>(x0 * c[k] - x1 * s[k]);
+        dst[i1] = from_f32<T>(x0 * s[k] + x1 * c[k]);
+    }
+    for (int i = tid; i < nh * (rd - rot); i += blockDim.x) {
+        const int h = h0 + i / (rd - rot), j = rot + i % (rd - rot);
+        q_wide[((size_t)t * n_heads + h) * wide + rank + j] = row[h * qh + d + j];
+    }
+    if (blockIdx.y != 0) return;
 
     // the lists of the grouped products: head h owns the rows h * T .. (h + 1) * T, in tiles of tile_rows
     if (t == 0) {
@@ -56,25 +88,6 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, const float* __restric
         if (tid == 0) n_tiles[0] = n_heads * per_head;
     }
     for (int h = tid; h < n_heads; h += blockDim.x) order[(size_t)h * n_tokens + t] = h * n_tokens + t;
-
-    // queries: the unrotated parts head by head, the rotated parts into the wide rows
-    for (int i = tid; i < n_heads * d; i += blockDim.x) {
-        const int h = i / d, j = i % d;
-        q_nope[((size_t)h * n_tokens + t) * d + j] = row[h * qh + j];
-    }
-    for (int i = tid; i < n_heads * half; i += blockDim.x) {
-        const int h = i / half, k = i % half;
-        const int i0 = style == 0 ? k : 2 * k, i1 = style == 0 ? k + half : 2 * k + 1;
-        const T* v = row + h * qh + d;
-        const float x0 = to_f32<T>(v[i0]), x1 = to_f32<T>(v[i1]);
-        T* dst = q_wide + ((size_t)t * n_heads + h) * wide + rank;
-        dst[i0] = from_f32<T>(x0 * c[k] - x1 * s[k]);
-        dst[i1] = from_f32<T>(x0 * s[k] + x1 * c[k]);
-    }
-    for (int i = tid; i < n_heads * (rd - rot); i += blockDim.x) {
-        const int h = i / (rd - rot), j = rot + i % (rd - rot);
-        q_wide[((size_t)t * n_heads + h) * wide + rank + j] = row[h * qh + d + j];
-    }
     if (!write_kv) return;
 
     // the cache row: normalised latent, rotated key part
@@ -189,10 +202,14 @@ RI_API int ri_latent_prepare(const void* proj, int dtype, int ld, const float* c
     if (style != 0 && style != 1) return fail("latent_prepare: unknown style %d", style);
     if (tile_rows <= 0 || n_heads <= 0 || d <= 0 || rank <= 0) return fail("latent_prepare: sizes");
     if ((long long)n_heads * n_tokens > 0x7fffffffLL) return fail("latent_prepare: %d heads x %d tokens exceed 2^31", n_heads, n_tokens);
+    const int groups = (n_heads + PREPARE_HEADS - 1) / PREPARE_HEADS;
+    if (groups > 65535) return fail("latent_prepare: %d heads exceed the grid limit", n_heads);
+    const int vec = dtype == RI_BF16 && d % 8 == 0 && rd % 8 == 0 && ld % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)q_nope % 16 == 0;
+    const dim3 grid(n_tokens, groups);
     cudaError_t e;
-#define RI_PREPARE(T) launch_dependent(latent_prepare_kernel<T>, n_tokens, 128, 0, stream, (const T*)proj, ld, cos_t, sin_t, \
+#define RI_PREPARE(T) launch_dependent(latent_prepare_kernel<T>, grid, dim3(128), (size_t)0, stream, (const T*)proj, ld, cos_t, sin_t, \
         c_w, eps, token_pos, token_seq, seq_slot, page_table, max_pages, (T*)cache, (T*)q_nope, (T*)q_wide, offsets, order, \
-        tiles, n_tiles, n_tokens, n_heads, d, rd, rank, rot, style, page_size, write_kv, tile_rows)
+        tiles, n_tiles, n_tokens, n_heads, d, rd, rank, rot, style, page_size, write_kv, tile_rows, vec)
     if (dtype == RI_F32) e = RI_PREPARE(float);
     else if (dtype == RI_BF16) e = RI_PREPARE(__nv_bfloat16);
     else return fail("latent_prepare: unknown dtype %d", dtype);

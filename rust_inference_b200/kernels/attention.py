@@ -133,13 +133,14 @@ def attention(qkv, cache_layer, out, ctx, *, n_heads, n_kv_heads, head_dim, scal
 
 # RI_B200_LATENT_ATTENTION=generic keeps the generic kernel for attention over a shared latent (for comparisons)
 _LATENT = os.environ.get("RI_B200_LATENT_ATTENTION", "mma")
-LATENT_TILE_KEYS, LATENT_MAX_SPLITS = 32, 16
+LATENT_TILE_KEYS = 32
 
 
-def latent_splits(n_ctas: int, longest: int) -> int:
+def latent_splits(n_ctas: int, longest: int, tile_rows: int) -> int:
     """Runs of keys per sequence for a step whose row tiles alone make n_ctas CTAs: as many as fill the SMs once
-    (the kernel holds one CTA per SM), never more than the longest sequence has key tiles."""
-    return max(1, min(LATENT_MAX_SPLITS, _sm_count() // max(1, n_ctas), -(-longest // LATENT_TILE_KEYS)))
+    (the kernel holds one CTA per SM, two of its smallest), never more than the longest sequence has key tiles."""
+    per_sm, most = (2, 32) if tile_rows <= 16 else (1, 16)
+    return max(1, min(most, per_sm * _sm_count() // max(1, n_ctas), -(-longest // LATENT_TILE_KEYS)))
 
 
 def latent_attention(q_wide, cache_layer, out, ctx, *, n_heads, key_dim, rank, scale):
@@ -151,12 +152,12 @@ def latent_attention(q_wide, cache_layer, out, ctx, *, n_heads, key_dim, rank, s
     rd = key_dim - rank
     if q_wide.dtype == torch.bfloat16 and _LATENT != "generic" and ops.latent_attention_mma_supports(rank, rd, ctx.page_size):
         n = q_wide.shape[0]
-        halves = 2 if rank > 256 else 1
         rows = ctx.max_new * n_heads
-        tiles = -(-rows // (128 if rows >= 128 else 64))            # the kernel's row tile (ri_latent_attention_mma_tile_rows)
+        tile_rows = ops.latent_attention_mma_tile_rows(rows, rank)
+        tiles = -(-rows // tile_rows)
         # a decode step's grid may depend on the batch size and the cache geometry only (captured steps)
         longest = ctx.page_table.shape[1] * ctx.page_size if ctx.all_single else ctx.max_len
-        splits = latent_splits(tiles * ctx.n_seqs * halves, longest)
+        splits = latent_splits(tiles * ctx.n_seqs, longest, tile_rows)
         part_o = part_ml = None
         if splits > 1:
             part_o = ctx.buffer("latent_part_o", (n * n_heads * splits * rank,), torch.float32)

@@ -746,6 +746,11 @@ def latent_attention_mma_supports(rank: int, rot_dim: int, page_size: int) -> bo
     return bool(load("latent_attention_mma").ri_latent_attention_mma_supports(c_int(rank), c_int(rot_dim), c_int(page_size)))
 
 
+def latent_attention_mma_tile_rows(rows: int, rank: int) -> int:
+    """Query rows a CTA of the kernel takes in a step whose longest run of new rows (tokens x heads) is `rows`."""
+    return int(load("latent_attention_mma").ri_latent_attention_mma_tile_rows(c_longlong(rows), c_int(rank)))
+
+
 def latent_attention_mma(q_wide: torch.Tensor, cache: torch.Tensor, page_table, seq_slot, seq_start, cu_seqlens,
                          out: torch.Tensor, *, n_seqs: int, max_new: int, n_heads: int, rank: int, rot_dim: int, scale: float,
                          n_splits: int = 1, part_o: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> torch.Tensor:

@@ -537,7 +537,8 @@ def test_the_command_line_on_a_vadodra_folder(models, tmp_path):
     assert len([l for l in p.stdout.splitlines() if l.strip()]) == 2 and "[L4]" in p.stderr + p.stdout
 
 
-@pytest.mark.parametrize("rank,rd,heads", [(64, 32, 8), (128, 64, 3), (256, 32, 5), (512, 64, 16), (512, 32, 1), (64, 64, 128)])
+@pytest.mark.parametrize("rank,rd,heads", [(64, 32, 8), (128, 64, 3), (256, 32, 5), (512, 64, 16), (512, 32, 1), (64, 64, 128),
+                                             (512, 64, 32), (256, 64, 24), (128, 32, 40)])
 def test_latent_attention_on_tensor_cores(rank, rd, heads):
     """The tensor-core kernel of attention over one cached row per position against plain softmax attention over the
     same rows: prompts of unequal length in one step (row tiles that end inside a token's heads), a continuation by a
