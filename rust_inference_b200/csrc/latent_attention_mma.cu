@@ -103,7 +103,8 @@ latent_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
     auto load_keys = [&](int kt, int stage) {
         const int j0 = kt * BN;
-        const int page = pages[j0 / PAGE];
+        int page = pages[j0 / PAGE];
+        if (!RI_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) page = 0;      // checked build: recorded, read from a page that exists
         const __nv_bfloat16* src = cache + ((size_t)page * PAGE + (j0 % PAGE)) * KD;
         const uint32_t dst = k_s + stage * (BN * ROW);
         for (int i = tid; i < BN * (KD / 8); i += THREADS) {

@@ -611,3 +611,54 @@ def test_latent_attention_on_tensor_cores(rank, rd, heads):
     run([0, 1], [150, 64], [50, 6])                       # continuations by portions
     run([1, 0, 2], [69, 199, 32], [1, 1, 1])              # decoding, the keys in runs
     run([2], [0], [1])                                    # the first token of a sequence alone
+
+
+def test_checked_build_stays_silent_and_skips_a_bad_slot(tmp_path):
+    """The checked build (indices that reach memory through a table are compared with their limits) runs a Vadodra
+    model in both precisions without a record; the heads' norm + rotation + cache-write kernel handed a slot beyond the
+    cache's slots records it and writes nothing.  In a process of its own: the build is chosen when the package is
+    imported."""
+    import os
+    import subprocess
+    import sys
+    import textwrap
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = textwrap.dedent("""
+        import sys, pathlib, tempfile, torch
+        sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+        import vadodra_models
+        from conftest import random_tokens, rel_err
+        from rust_inference_b200.engine.engine import Engine
+        from rust_inference_b200.kernels import build, ops
+        from rust_inference_b200.parts.rope import rope_tables
+        assert build.CHECKED and build.library_path("latent").endswith("checked/libri_latent.so")
+        model = vadodra_models.make(pathlib.Path(tempfile.mkdtemp()), "C")
+        toks = random_tokens(150, model.cfg["vocab"], 3)
+        want = model.plain_logits(toks)
+        for dtype in ("float32", "bfloat16"):
+            eng = Engine.from_pretrained(model.folder, dtype=dtype, max_tokens=512, n_slots=3)
+            s = eng.alloc_slot()
+            head = eng.step([s], [toks[:140]], "all").cpu()
+            tail = torch.cat([eng.step([s], [[t]], "last").cpu() for t in toks[140:]])
+            assert rel_err(torch.cat([head, tail]), want) <= (1e-4 if dtype == "float32" else 6e-2)
+            eng.check_device_status()
+        assert ops.bounds_report() == []
+        ops.bounds_set_limits(0, 3, 8)
+        heads, kvh, hd = 2, 1, 16
+        qk = torch.randn(1, (heads + kvh) * hd, device="cuda")
+        cos, sin = rope_tables(hd, 100.0, 8)
+        kc = torch.full((8, kvh, 64, hd), 5.0, device="cuda")
+        vc = torch.full((8, kvh, 64, hd), 5.0, device="cuda")
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+        ops.rope_normed_cache_write(qk, torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda(), None, None, 1e-6, i32([0]),
+                                    i32([0]), i32([9]), torch.zeros(3, 2, dtype=torch.int32, device="cuda"), kc, vc, n_heads=heads,
+                                    n_kv_heads=kvh, head_dim=hd, page_size=64, style=1, write_kv=True, values_from_keys=True)
+        torch.cuda.synchronize()
+        assert float((kc - 5.0).abs().max()) == 0.0 and float((vc - 5.0).abs().max()) == 0.0
+        rep = ops.bounds_report()
+        assert rep and rep[0][0] == "elementwise" and rep[0][1] == "a cache slot that does not exist" and rep[0][2] == 9, rep
+        print("checked ok")
+    """).format(root=root, tests=os.path.join(root, "tests"))
+    env = dict(os.environ, RI_B200_CHECK_BOUNDS="1")
+    p = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0 and "checked ok" in p.stdout, p.stderr[-3000:]
