@@ -734,6 +734,113 @@ rope_normed_cache_write_kernel(T* __restrict__ qkv, int ld, const float* __restr
     }
     for (int d = rot + lane; d < hd; d += 32) dst[d] = from_f32<T>(x[d]);
 }
+// The same for bf16 heads of up to 256 channels (a multiple of 8), 16 bytes per lane: lane l of the warp holds the
+// head's channels 8l .. 8l + 7 in registers, the sum of squares goes through shuffles, and the head is read and
+// written once, 16 bytes at a time.  Adjacent pairs (style 1) lie inside a lane; for the halves pairing (style 0)
+// a channel's partner lies in lane l ^ (rot / 16), which needs rot to be 16 times a power of two.  rot % 8 == 0.
+__global__ void __launch_bounds__(NORMED_ROPE_WARPS * 32)
+rope_normed_cache_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, const float* __restrict__ q_w,
+                                   const float* __restrict__ k_w, float eps, const int* __restrict__ token_pos,
+                                   const int* __restrict__ token_seq, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ page_table, int max_pages, __nv_bfloat16* __restrict__ kcache,
+                                   __nv_bfloat16* __restrict__ vcache, int n_tokens, int n_heads, int n_kv_heads, int hd,
+                                   int page_size, int style, int write_kv, int rot, int v_hd, int v_from_k) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = n_heads + n_kv_heads + (v_from_k ? 0 : n_kv_heads);
+    const long long item = (long long)blockIdx.x * NORMED_ROPE_WARPS + warp;
+    let_next_kernel_start();
+    if (item >= (long long)n_tokens * heads) return;
+    const int t = (int)(item / heads), h = (int)(item % heads);
+    if (h >= n_heads && !write_kv) return;
+    const int pos = token_pos[t];                     // positions, slots, pages and angles: fixed before the step
+    const int half = rot >> 1;
+    const float* c = cos_t + (size_t)pos * half;
+    const float* s = sin_t + (size_t)pos * half;
+    size_t cache_row = 0;
+    if (h >= n_heads) {
+        const int slot = seq_slot[token_seq[t]];
+        if (!RI_IN_LIMIT(slot, RI_LIMIT_SLOTS, RI_CHECK_SLOT) || !RI_IN_RANGE(pos / page_size, max_pages, RI_CHECK_PAGE_INDEX)) return;
+        const int page = page_table[(size_t)slot * max_pages + pos / page_size];
+        if (!RI_IN_LIMIT(page, RI_LIMIT_PAGES, RI_CHECK_PAGE)) return;
+        cache_row = (size_t)page * n_kv_heads * page_size + (pos % page_size);
+    }
+    const int ch = 8 * lane;
+    // this lane's angles (loaded before the wait: the tables are written once)
+    float cs[8], sn[8];
+    int n_ang = 0, a0 = 0;                            // style 1: 4 angles from ch / 2; style 0: 8 from ch % half
+    if (ch < rot) {
+        n_ang = style == 1 ? 4 : 8;
+        a0 = style == 1 ? ch >> 1 : ch % half;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i += 4) {
+        if (i < n_ang) {
+            *reinterpret_cast<float4*>(cs + i) = *reinterpret_cast<const float4*>(c + a0 + i);
+            *reinterpret_cast<float4*>(sn + i) = *reinterpret_cast<const float4*>(s + a0 + i);
+        } else {
+            cs[i] = cs[i + 1] = cs[i + 2] = cs[i + 3] = 1.f;
+            sn[i] = sn[i + 1] = sn[i + 2] = sn[i + 3] = 0.f;
+        }
+    }
+    const bool is_q = h < n_heads;
+    const float* w = is_q ? q_w : k_w;
+    float wv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) wv[i] = 1.f;
+    if (w != nullptr && ch < hd && h < n_heads + n_kv_heads) {
+        *reinterpret_cast<float4*>(wv) = *reinterpret_cast<const float4*>(w + ch);
+        *reinterpret_cast<float4*>(wv + 4) = *reinterpret_cast<const float4*>(w + ch + 4);
+    }
+    wait_for_previous_kernels();          // the projections come from the previous kernel
+    __nv_bfloat16* row = qkv + (size_t)t * ld;
+    if (h >= n_heads + n_kv_heads) {      // a value head of its own: copy
+        const int kh = h - n_heads - n_kv_heads;
+        if (ch < v_hd)
+            *reinterpret_cast<uint4*>(vcache + (cache_row + (size_t)kh * page_size) * v_hd + ch) =
+                *reinterpret_cast<const uint4*>(row + (size_t)(n_heads + n_kv_heads) * hd + (size_t)kh * v_hd + ch);
+        return;
+    }
+    const int kh = h - n_heads;
+    __nv_bfloat16* src = row + (size_t)h * hd;
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = 0.f;
+    if (ch < hd) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + ch);
+        if (!is_q && v_from_k) *reinterpret_cast<uint4*>(vcache + (cache_row + (size_t)kh * page_size) * hd + ch) = raw;
+        unpack8(raw, x);
+    }
+    if (w != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = x[i] * scale * wv[i];
+    }
+    float y[8];
+    if (style == 1) {
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {     // lanes beyond the rotated channels have cos 1, sin 0
+            y[2 * p] = x[2 * p] * cs[p] - x[2 * p + 1] * sn[p];
+            y[2 * p + 1] = x[2 * p] * sn[p] + x[2 * p + 1] * cs[p];
+        }
+    } else {
+        const int partner = half >> 3;    // lanes between a channel and its partner
+        const bool low = ch < half;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float other = __shfl_xor_sync(0xffffffffu, x[i], partner);
+            y[i] = ch >= rot ? x[i] : (low ? x[i] * cs[i] - other * sn[i] : other * sn[i] + x[i] * cs[i]);
+        }
+    }
+    if (ch < hd) {
+        __nv_bfloat16* dst = is_q ? src : kcache + (cache_row + (size_t)kh * page_size) * hd;
+        *reinterpret_cast<uint4*>(dst + ch) = pack8(y);
+    }
+}
 }  // namespace
 
 RI_API int ri_rope_normed_cache_write(void* qkv, int dtype, int ld, const float* cos_t, const float* sin_t,
@@ -754,6 +861,19 @@ RI_API int ri_rope_normed_cache_write(void* qkv, int dtype, int ld, const float*
     const long long items = (long long)n_tokens * heads;
     const unsigned blocks = (unsigned)((items + NORMED_ROPE_WARPS - 1) / NORMED_ROPE_WARPS);
     cudaError_t e;
+    const int lanes_apart = rot / 16;     // halves pairing: a channel's partner sits this many lanes away
+    const bool pairing_ok = style == 1 || (rot % 16 == 0 && (lanes_apart & (lanes_apart - 1)) == 0);
+    const bool aligned = hd % 8 == 0 && hd <= 256 && v_hd % 8 == 0 && v_hd <= 256 && rot % 8 == 0 && ld % 8 == 0 &&
+                         (uintptr_t)qkv % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 &&
+                         (uintptr_t)cos_t % 16 == 0 && (uintptr_t)sin_t % 16 == 0 && (q_w == nullptr || (uintptr_t)q_w % 16 == 0) &&
+                         (k_w == nullptr || (uintptr_t)k_w % 16 == 0);
+    if (dtype == RI_BF16 && aligned && pairing_ok) {
+        e = launch_dependent(rope_normed_cache_write_vec_kernel, blocks, NORMED_ROPE_WARPS * 32, 0, stream, (__nv_bfloat16*)qkv, ld,
+                             cos_t, sin_t, q_w, k_w, eps, token_pos, token_seq, seq_slot, page_table, max_pages,
+                             (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, n_tokens, n_heads, n_kv_heads, hd, page_size, style,
+                             write_kv, rot, v_hd, v_from_k);
+        return check_launch(e, "rope_normed_cache_write");
+    }
 #define RI_NORMED_ROPE(T) launch_dependent(rope_normed_cache_write_kernel<T>, blocks, NORMED_ROPE_WARPS * 32, smem, stream, \
         (T*)qkv, ld, cos_t, sin_t, q_w, k_w, eps, token_pos, token_seq, seq_slot, page_table, max_pages, (T*)kcache, \
         (T*)vcache, n_tokens, n_heads, n_kv_heads, hd, page_size, style, write_kv, rot, v_hd, v_from_k)

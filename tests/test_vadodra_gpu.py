@@ -54,17 +54,21 @@ def test_layer_norm_kernel(dtype, rows, width):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("style", [0, 1])
-@pytest.mark.parametrize("heads,kvh,hd,rot", [(4, 2, 32, 8), (3, 3, 24, 24), (1, 1, 80, 2), (8, 1, 128, 64)])
-def test_normed_rotation_and_cache_write(dtype, style, heads, kvh, hd, rot):
+@pytest.mark.parametrize("heads,kvh,hd,rot,own_values", [(4, 2, 32, 8, False), (3, 3, 24, 24, False), (1, 1, 80, 2, False),
+                                                         (8, 1, 128, 64, False), (2, 2, 256, 256, False), (4, 1, 64, 16, False),
+                                                         (5, 5, 40, 24, False), (3, 1, 64, 32, True), (2, 2, 20, 10, True)])
+def test_normed_rotation_and_cache_write(dtype, style, heads, kvh, hd, rot, own_values):
     """RMS norm of every q and k head, rotation of the first channels in either pairing, the keys into the
-    paged cache and the keys as projected into the value cache, at positions on both sides of a page border
-    with pages out of order."""
+    paged cache and the keys as projected into the value cache (or, with own_values, value columns of their own,
+    copied), at positions on both sides of a page border with pages out of order.  bfloat16 heads whose sizes allow
+    take the form of the kernel that moves 16 bytes per lane; the others, and float32, the plain one."""
     from rust_inference_b200.kernels import ops
     from rust_inference_b200.parts.rope import rope_tables
     g = torch.Generator().manual_seed(hd + rot + style)
     page, pos = 64, torch.tensor([62, 63, 64, 65, 130, 0])
     n = pos.numel()
-    qk = (torch.randn(n, (heads + kvh) * hd, generator=g) * 1.7).to(dtype)
+    cols = (heads + kvh) * hd + (kvh * hd if own_values else 0)
+    qk = (torch.randn(n, cols, generator=g) * 1.7).to(dtype)
     qw, kw = 1 + 0.3 * torch.randn(hd, generator=g), 1 + 0.3 * torch.randn(hd, generator=g)
     cos, sin = rope_tables(rot, 321.0, 200, exact_angles=True, scaling_factor=2.5)
     table = torch.tensor([[5, 2, 7, 1]], dtype=torch.int32)
@@ -74,18 +78,20 @@ def test_normed_rotation_and_cache_write(dtype, style, heads, kvh, hd, rot):
     ops.rope_normed_cache_write(dev, d(torch.from_numpy(cos)), d(torch.from_numpy(sin)), d(qw), d(kw), 1e-5, d(pos.int()),
                                 d(torch.zeros(n, dtype=torch.int32)), i32([0]), d(table), kc, vc, n_heads=heads,
                                 n_kv_heads=kvh, head_dim=hd, page_size=page, style=style, write_kv=True, rot_dims=rot,
-                                values_from_keys=True)
+                                values_from_keys=not own_values)
     turn = plain_vadodra.rotate_halves if style == 0 else plain_vadodra.rotate_adjacent
     q0 = qk[:, :heads * hd].double().view(n, heads, hd)
-    k0 = qk[:, heads * hd:].double().view(n, kvh, hd)
+    k0 = qk[:, heads * hd:(heads + kvh) * hd].double().view(n, kvh, hd)
+    values = qk[:, (heads + kvh) * hd:] if own_values else qk[:, heads * hd:]
     q_want = turn(plain_vadodra.rms_norm(q0, qw.double(), 1e-5), pos, 321.0, rot, 2.5)
     k_want = turn(plain_vadodra.rms_norm(k0, kw.double(), 1e-5), pos, 321.0, rot, 2.5)
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     assert rel_err(dev[:, :heads * hd], q_want.reshape(n, -1)) < tol
+    assert torch.equal(dev[:, heads * hd:].cpu(), qk[:, heads * hd:])          # k (and v) columns are left as they came
     for t in range(n):
         p = int(pos[t])
         assert rel_err(kc[table[0, p // page], :, p % page].reshape(1, -1), k_want[t].reshape(1, -1)) < tol
-        assert torch.equal(vc[table[0, p // page], :, p % page].cpu().reshape(-1), qk[t, heads * hd:])
+        assert torch.equal(vc[table[0, p // page], :, p % page].cpu().reshape(-1), values[t])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
