@@ -43,10 +43,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 // The thread's row (TMEM lane) times the tile's features, 16 at a time.
+// `spread` (plain form only): the result is rounded to bf16 and the row goes to out + out_row * out_ld instead of
+// out + row * n_feat (rows of a wider matrix, in another order: see the kernel).
 template <bool GATE>
 __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, int f0, int n_feat, bool aligned,
-                                           void* __restrict__ out_) {
+                                           void* __restrict__ out_, bool spread = false, size_t out_row = 0, int out_ld = 0) {
     constexpr int FEATS = GATE ? TM_ROWS / 2 : TM_ROWS;
+    const bool narrow = GATE || spread;                     // the result is bf16
 #pragma unroll 1
     for (int c0 = 0; c0 < FEATS; c0 += 16) {
         if (f0 + c0 >= n_feat) break;                       // uniform over the warp
@@ -55,7 +58,7 @@ __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, 
         if (GATE) tmem_ld16(trow + TM_ROWS / 2 + c0, u);
         tmem_wait_ld();
         if (!row_ok) continue;
-        const size_t o0 = (size_t)row * n_feat + f0 + c0;
+        const size_t o0 = spread ? out_row * (size_t)out_ld + f0 + c0 : (size_t)row * n_feat + f0 + c0;
         float r[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -63,7 +66,7 @@ __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, 
             r[j] = GATE ? silu_to_bf16(a) * __uint_as_float(u[j]) : a;
         }
         if (aligned && f0 + c0 + 16 <= n_feat) {
-            if (GATE) {
+            if (narrow) {
                 __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out_) + o0;
                 uint4 lo, hi;
                 lo.x = pack_bf16x2(r[0], r[1]);  lo.y = pack_bf16x2(r[2], r[3]);
@@ -80,7 +83,7 @@ __device__ __forceinline__ void write_tile(uint32_t trow, int row, bool row_ok, 
         } else {
             for (int j = 0; j < 16; ++j)
                 if (f0 + c0 + j < n_feat) {
-                    if (GATE) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
+                    if (narrow) reinterpret_cast<__nv_bfloat16*>(out_)[o0 + j] = __float2bfloat16_rn(r[j]);
                     else reinterpret_cast<float*>(out_)[o0 + j] = r[j];
                 }
         }
@@ -92,7 +95,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out_, const int* offsets,
                       const int* tiles, const int* n_tiles, int n_feat, int K, int stages,
-                      int* status) {
+                      int* status, int spread_groups, int spread_ld) {
+    // spread_groups > 0 (plain form): out is bf16 with rows of spread_ld values, and row i of group e goes to row
+    // i * spread_groups + e of it (the groups' rows interleaved: a group is a head, a row a token, and out a matrix
+    // [tokens, heads, spread_ld] whose first n_feat channels per head are written).
     constexpr int FEATS = GATE ? TM_ROWS / 2 : TM_ROWS;        // output features per tile
     constexpr int X_BYTES = TM_TOK * BLOCK_K * 2;
     constexpr int TMEM_COLS = 2 * TM_ROWS;                     // two accumulator buffers
@@ -221,7 +227,8 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         }
     } else {
         const int lane_base = (warp & 3) * 32;
-        const bool aligned = n_feat % 8 == 0;                      // rows of `out` keep 16-byte alignment
+        const bool spread = !GATE && spread_groups > 0;
+        const bool aligned = spread ? spread_ld % 8 == 0 : n_feat % 8 == 0;      // rows of `out` keep 16-byte alignment
         for (int i = 0; i < my_tiles; ++i) {
             int e, row0, f0;
             tile_coords(i, e, row0, f0);
@@ -236,7 +243,8 @@ moe_grouped_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (!landed || abort_flag) break;
             const int row = row0 + lane_base + lane;
             const uint32_t trow = tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(buf * TM_ROWS);
-            write_tile<GATE>(trow, row, row < row_end, f0, n_feat, aligned, out_);
+            write_tile<GATE>(trow, row, row < row_end, f0, n_feat, aligned, out_, spread,
+                             spread ? (size_t)(row - offsets[e]) * spread_groups + e : 0, spread_ld);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
@@ -265,7 +273,8 @@ int sm_count() {
 
 template <bool GATE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx, void* out, const int* offsets,
-           const int* tiles, const int* n_tiles, int n_pairs, int experts, int N, int K, int* status, cudaStream_t stream) {
+           const int* tiles, const int* n_tiles, int n_pairs, int experts, int N, int K, int* status, cudaStream_t stream,
+           int spread_groups = 0, int spread_ld = 0) {
     const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
     int stages = SMEM_BUDGET / STAGE_BYTES;
     if (stages > total_kb) stages = total_kb;
@@ -281,7 +290,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
     long long ctas = sm_count();
     if (ctas > most) ctas = most;
     cudaError_t e = launch_dependent(kernel, dim3((unsigned)ctas), dim3(THREADS), smem, stream, mw, mw2, mx, out, offsets,
-                                     tiles, n_tiles, N, K, stages, status);
+                                     tiles, n_tiles, N, K, stages, status, spread_groups, spread_ld);
     return check_launch(e, "moe_grouped_tcgen05");
 }
 
@@ -303,6 +312,21 @@ RI_API int ri_moe_grouped_tcgen05(const void* map_x, const void* map_w, const vo
     const CUtensorMap& mw2 = *reinterpret_cast<const CUtensorMap*>(gate ? map_w2 : map_w);
     if (gate) return launch<true>(mw, mw2, mx, out, offsets, tiles, n_tiles, n_pairs, experts, N, K, status, stream);
     return launch<false>(mw, mw2, mx, out, offsets, tiles, n_tiles, n_pairs, experts, N, K, status, stream);
+}
+
+// The plain form with its result rounded to bf16 and the groups' rows interleaved: row i of group e goes to
+// out + (i * experts + e) * out_ld (out: bf16 [rows per group, experts, out_ld], of which the first N channels of every
+// (row, group) are written).  For per-head maps whose result is wanted token by token.
+RI_API int ri_moe_grouped_tcgen05_spread(const void* map_x, const void* map_w, void* out, int out_ld, const int* offsets,
+                                         const int* tiles, const int* n_tiles, int n_pairs, int experts, int N, int K,
+                                         int* status, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (K <= 0 || K % 8) return fail("moe_grouped_tcgen05: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+    if (out_ld < N) return fail("moe_grouped_tcgen05: rows of %d values cannot hold %d", out_ld, N);
+    if ((long long)experts * N > 0x7fffffffLL) return fail("moe_grouped_tcgen05: %d experts of %d rows exceed the index range", experts, N);
+    const CUtensorMap& mx = *reinterpret_cast<const CUtensorMap*>(map_x);
+    const CUtensorMap& mw = *reinterpret_cast<const CUtensorMap*>(map_w);
+    return launch<false>(mw, mw, mx, out, offsets, tiles, n_tiles, n_pairs, experts, N, K, status, stream, experts, out_ld);
 }
 
 RI_DEFINE_LAST_ERROR()

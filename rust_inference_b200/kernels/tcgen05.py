@@ -188,3 +188,21 @@ def grouped_gemm(x: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offset
           c_void_p(_stacked_map(w2).data_ptr() if gate else 0), _p(out), c_int(1 if gate else 0), _p(offsets), _p(tiles),
           _p(n_tiles), c_int(n_pairs), c_int(experts), c_int(n), c_int(k), c_void_p(st.data_ptr()), _stream())
     return out
+
+
+def grouped_gemm_spread(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, out_ld: int, offsets, tiles, n_tiles, *, n_pairs: int):
+    """The plain grouped product with its result rounded to bfloat16 and the groups' rows interleaved: for every
+    group e (rows offsets[e]..offsets[e+1] of x, all groups equally many), row i of the group times w[e]^T goes to
+    out[i, e, :N], out being bfloat16 [rows per group, groups, out_ld].  For per-head maps (a head = a group) whose
+    result is wanted token by token, inside wider rows."""
+    _need_cuda(x, w, out, offsets, tiles, n_tiles)
+    groups, n, k = w.shape
+    _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and x.is_contiguous()
+          and w.is_contiguous() and out.is_contiguous() and x.shape == (n_pairs, k), "grouped_gemm_spread: bf16, x [pairs, K]")
+    _need(n_pairs % groups == 0 and out_ld >= n and out.numel() >= n_pairs * out_ld, "grouped_gemm_spread: out too small")
+    map_x = _x_map(x, 128)
+    st = status_word()
+    _call("moe_tcgen05", "ri_moe_grouped_tcgen05_spread", c_void_p(map_x.data_ptr()), c_void_p(_stacked_map(w).data_ptr()),
+          _p(out), c_int(out_ld), _p(offsets), _p(tiles), _p(n_tiles), c_int(n_pairs), c_int(groups), c_int(n), c_int(k),
+          c_void_p(st.data_ptr()), _stream())
+    return out

@@ -153,9 +153,13 @@ class LatentAttention(Mixer):
                            n_heads=H, head_dim=d, rot_dim=rd, rank=kr, rot_dims=pos.rot_dims, style=pos.style,
                            page_size=ctx.page_size, write_kv=writes_cache, tile_rows=tile_rows)
         # the queries into the latent space, head by head
-        q_lat = ctx.buffer("latent_q_lat", (rows, kr), torch.float32)
-        self._grouped(q_nope, self.w_uk_t, q_lat, lists, rows)
-        ops.latent_widen(q_lat, q_wide, n_tokens=n, n_heads=H, rank=kr, rot_dim=rd)
+        if fast:
+            # on the tensor cores the product's epilogue rounds and writes the wide rows itself
+            tcgen05.grouped_gemm_spread(q_nope, self.w_uk_t, q_wide, self.wide, offsets, tiles, n_tiles, n_pairs=rows)
+        else:
+            q_lat = ctx.buffer("latent_q_lat", (rows, kr), torch.float32)
+            self._grouped(q_nope, self.w_uk_t, q_lat, lists, rows)
+            ops.latent_widen(q_lat, q_wide, n_tokens=n, n_heads=H, rank=kr, rot_dim=rd)
         # attention of all heads over the one cached row per position; the weighted latents head by head
         o_lat = ctx.buffer("latent_o_lat", (rows, kr), self.dtype)              # [heads, T, kv_rank]
         attn_kernels.latent_attention(q_wide, cache_layer, o_lat, ctx, n_heads=H, key_dim=self.wide, rank=kr,
